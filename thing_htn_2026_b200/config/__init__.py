@@ -2,6 +2,7 @@ from .base import (ConfigError, LayerSpec, ModelConfig, ModelPlan, PartSpec, Sch
                    read_config_json)
 from .named import named_config_json, named_configs
 from .bunudra import BunudraConfig
+from .ditilix import DitilixConfig
 from .lanilix import LanilixConfig
 from .qwen3 import Qwen3Config
 from .registry import (architecture_of, config_from_dict, known_architectures, load_config,
@@ -9,6 +10,6 @@ from .registry import (architecture_of, config_from_dict, known_architectures, l
 
 __all__ = [
     "ConfigError", "LayerSpec", "ModelConfig", "ModelPlan", "PartSpec", "ScheduleEntry",
-    "read_config_json", "Qwen3Config", "LanilixConfig", "BunudraConfig", "named_config_json", "named_configs", "architecture_of", "config_from_dict",
+    "read_config_json", "Qwen3Config", "LanilixConfig", "BunudraConfig", "DitilixConfig", "named_config_json", "named_configs", "architecture_of", "config_from_dict",
     "known_architectures", "load_config", "model_class_for", "register_architecture",
 ]

@@ -63,11 +63,13 @@ def _decoder_model():
 
 def _register_builtin() -> None:
     from .bunudra import BunudraConfig
+    from .ditilix import DitilixConfig
     from .lanilix import LanilixConfig
     from .qwen3 import Qwen3Config
     register_architecture(Qwen3Config.architecture, Qwen3Config, _decoder_model)
     register_architecture(LanilixConfig.architecture, LanilixConfig, _decoder_model)
     register_architecture(BunudraConfig.architecture, BunudraConfig, _decoder_model)
+    register_architecture(DitilixConfig.architecture, DitilixConfig, _decoder_model)
 
 
 _register_builtin()

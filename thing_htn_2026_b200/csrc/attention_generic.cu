@@ -14,7 +14,8 @@
 // instead, a row sees the keys j <= p of its own chunk only: floor(j / C) = floor(p / C),
 // chunks counted from position 0 of the sequence.  Values may have a size of their own
 // (kv.value_dim); the output then has that size per head.  exact_weights keeps e in float32
-// where it multiplies V.
+// where it multiplies V.  A ScoreShape (common.cuh) multiplies the scores of a row by a factor
+// that grows with the logarithm of its position and caps them with a tanh before the softmax.
 #include <math.h>
 
 #include "common.cuh"
@@ -25,7 +26,8 @@ template <typename T, int PER_LANE>
 __global__ void attention_generic_kernel(T* __restrict__ out, const T* __restrict__ q,
                                          const int* __restrict__ row_slot, const int* __restrict__ row_pos,
                                          PagedKV kv, int n_rows, int n_q, float scale, int window,
-                                         int keep_first, int chunk, int exact_weights, int* __restrict__ err) {
+                                         int keep_first, int chunk, int exact_weights, ScoreShape shape,
+                                         int* __restrict__ err) {
     pdl_launch_dependents();
     pdl_wait();
     const int lane = threadIdx.x & 31;
@@ -36,6 +38,7 @@ __global__ void attention_generic_kernel(T* __restrict__ out, const T* __restric
     const int kvh = h / (n_q / kv.n_kv);
     const int pos = row_pos[m];
     const int* pages = kv.block_table + (size_t)row_slot[m] * kv.bt_stride;
+    scale *= shape.row_factor(pos);
 
     float qv[PER_LANE], acc[PER_LANE];
 #pragma unroll
@@ -72,7 +75,7 @@ __global__ void attention_generic_kernel(T* __restrict__ out, const T* __restric
             const int d = lane + 32 * i;
             if (d < D) dot += qv[i] * to_f32<T>(k_page[in_page + d]);
         }
-        const float s = warp_sum(dot) * scale;
+        const float s = shape.capped(warp_sum(dot) * scale);
         const float new_max = fmaxf(run_max, s);
         const float correction = expf(run_max - new_max);  // 0 on the first key
         const float e = expf(s - new_max);
@@ -94,15 +97,15 @@ __global__ void attention_generic_kernel(T* __restrict__ out, const T* __restric
 
 template <typename T>
 static int launch_generic(void* out, const void* q, const int* row_slot, const int* row_pos, PagedKV kv, int n_rows,
-                          int n_q, float scale, int window, int keep_first, int chunk, int exact_weights, int* err,
-                          cudaStream_t stream) {
+                          int n_q, float scale, int window, int keep_first, int chunk, int exact_weights,
+                          ScoreShape shape, int* err, cudaStream_t stream) {
     const int warps = 4;
     const long long units = (long long)n_rows * n_q;
     const unsigned blocks = (unsigned)((units + warps - 1) / warps);
     const int per_lane = (max(kv.head_dim, kv.value_dim) + 31) / 32;
 #define LAUNCH(N)                                                                                                  \
     thn_launch(attention_generic_kernel<T, N>, blocks, warps * 32, 0, stream, (T*)out, (const T*)q, row_slot, row_pos, kv, \
-                                                                      n_rows, n_q, scale, window, keep_first, chunk, exact_weights, err)
+                                                                      n_rows, n_q, scale, window, keep_first, chunk, exact_weights, shape, err)
     if (per_lane <= 1) LAUNCH(1);
     else if (per_lane <= 2) LAUNCH(2);
     else if (per_lane <= 4) LAUNCH(4);
@@ -115,12 +118,12 @@ static int launch_generic(void* out, const void* q, const int* row_slot, const i
 // q [n_rows, n_q * head_dim], out [n_rows, n_q * value_dim]; the keys of a row are positions
 // [.., row_pos] of the sequence in row_slot, already in the cache.  window <= 0 means all keys
 // (keep_first is then without effect); chunk > 0: only the keys of the row's own chunk;
-// value_dim 0: values of the keys' size.
+// value_dim 0: values of the keys' size; softcap, temp_coef, temp_every: the ScoreShape (0: none).
 THN_API int thn_attention_generic(void* out, const void* q, const int* row_slot, const int* row_pos,
                                   const void* kv_base, const int* block_table, int bt_stride, int n_kv,
                                   int page_size, int head_dim, int value_dim, int n_rows, int n_q, float scale,
-                                  int window, int keep_first, int chunk, int exact_weights, int dtype, int* err,
-                                  cudaStream_t stream) {
+                                  int window, int keep_first, int chunk, int exact_weights, float softcap,
+                                  float temp_coef, int temp_every, int dtype, int* err, cudaStream_t stream) {
     THN_CHECK_ARG(n_rows >= 0 && n_q > 0 && n_kv > 0 && page_size > 0, "attention_generic: bad sizes");
     THN_CHECK_ARG(n_q % n_kv == 0, "attention_generic: %d query heads are not a multiple of %d kv heads", n_q, n_kv);
     THN_UNSUPPORTED_IF(head_dim <= 0 || head_dim > 32 * kGenericMaxPerLane || value_dim < 0 ||
@@ -128,11 +131,13 @@ THN_API int thn_attention_generic(void* out, const void* q, const int* row_slot,
                        "attention_generic: head_dim %d or value_dim %d not in [1, %d]", head_dim, value_dim,
                        32 * kGenericMaxPerLane);
     THN_CHECK_ARG(chunk <= 0 || keep_first <= 0, "attention_generic: kept first keys go with a window, not with chunks");
+    THN_CHECK_ARG(softcap >= 0.f && temp_every >= 0, "attention_generic: a score cap and a temperature period are not negative");
     if (n_rows == 0) return THN_OK;
+    const ScoreShape shape{softcap, temp_coef, temp_every};
     PagedKV kv{kv_base, block_table, bt_stride, n_kv, page_size, head_dim, value_dim == head_dim ? 0 : value_dim};
-    if (dtype == THN_F32) return launch_generic<float>(out, q, row_slot, row_pos, kv, n_rows, n_q, scale, window, keep_first, chunk, exact_weights, err, stream);
+    if (dtype == THN_F32) return launch_generic<float>(out, q, row_slot, row_pos, kv, n_rows, n_q, scale, window, keep_first, chunk, exact_weights, shape, err, stream);
     if (dtype == THN_BF16)
-        return launch_generic<__nv_bfloat16>(out, q, row_slot, row_pos, kv, n_rows, n_q, scale, window, keep_first, chunk, exact_weights, err, stream);
+        return launch_generic<__nv_bfloat16>(out, q, row_slot, row_pos, kv, n_rows, n_q, scale, window, keep_first, chunk, exact_weights, shape, err, stream);
     THN_CHECK_ARG(false, "attention_generic: unknown dtype %d", dtype);
     return THN_OK;
 }

@@ -26,8 +26,10 @@ struct KeyWindow {
     // 1: as two bfloat16 parts, P = hi + lo with lo = P - hi rounded (two products), which keeps
     // sixteen bits of every weight.
     int split_weights;
-    __host__ __device__ KeyWindow(int s = 0, int k = 0, int c = 0, int split = 0)
-        : size(s), keep(s > 0 ? k : 0), chunk(c), split_weights(split) {}
+    // What happens to a score between the scale and the softmax (common.cuh); inactive by default.
+    ScoreShape shape;
+    __host__ __device__ KeyWindow(int s = 0, int k = 0, int c = 0, int split = 0, ScoreShape sh = ScoreShape{0.f, 0.f, 0})
+        : size(s), keep(s > 0 ? k : 0), chunk(c), split_weights(split), shape(sh) {}
     __host__ __device__ operator int() const { return size; }
     // first position that the query at `pos` sees, kept first positions aside
     __host__ __device__ int first_visible(int pos) const {
@@ -125,6 +127,26 @@ __device__ __forceinline__ void pv_tile(float (&o)[D / 8][4], const uint32_t (&p
         }
     }
 }
+
+// A row's scores on their way into the log2 domain.  Without a cap: s * mul with
+// mul = scale * log2(e) * factor(position).  With a cap c: c log2(e) * tanh(s * mul), where
+// mul = scale * factor(position) / c.
+struct RowScore {
+    float mul, post;      // post 0: no cap
+    __device__ __forceinline__ RowScore(const ScoreShape& shape, float scale_log2, int pos) {
+        const float f = scale_log2 * shape.row_factor(pos);
+        if (shape.cap > 0.f) {
+            mul = f / (kLog2e * shape.cap);
+            post = shape.cap * kLog2e;
+        } else {
+            mul = f;
+            post = 0.f;
+        }
+    }
+    __device__ __forceinline__ float operator()(float s) const {
+        return post > 0.f ? post * tanh_by_exp2(s * mul) : s * mul;
+    }
+};
 
 // Online-softmax state of the two rows a thread owns (row g = lane / 4 and row g + 8), in
 // the log2 domain.  l holds this thread's share of the row sum until finish().
@@ -265,6 +287,7 @@ __global__ void __launch_bounds__(kPrefillThreads) attention_prefill_kernel(
     const int my_pos[2] = {pos0 + warp * 16 + g, pos0 + warp * 16 + g + 8};
     const int my_chunk_start[2] = {window.chunk > 0 ? my_pos[0] / window.chunk * window.chunk : 0,
                                    window.chunk > 0 ? my_pos[1] / window.chunk * window.chunk : 0};
+    const RowScore my_score[2] = {RowScore(window.shape, scale_log2, my_pos[0]), RowScore(window.shape, scale_log2, my_pos[1])};
 
     for (int visit = 0; visit < n_visits; ++visit) {
         const int t = tile_of(visit);
@@ -284,7 +307,7 @@ __global__ void __launch_bounds__(kPrefillThreads) attention_prefill_kernel(
             for (int n = 0; n < 8; ++n)
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
-                    float v = s[n][i] * scale_log2;
+                    float v = my_score[i >> 1](s[n][i]);
                     if (need_mask) {
                         const int key = key0 + n * 8 + tq * 2 + (i & 1);
                         const int p = my_pos[i >> 1];
@@ -461,6 +484,7 @@ __global__ void __launch_bounds__(kThreads) attention_decode_kernel(
     const int* pages = kv.block_table + (size_t)row_slot[b] * kv.bt_stride;
 
     const int first_key = window.first_visible(pos);
+    const RowScore score(window.shape, scale_log2, pos);     // the rows of the tile are the heads of one position
     const int t_first = first_key / kTile, t_last = pos / kTile;
     // Key tiles are counted in the order they are visited: those of the kept first positions that
     // lie before the window's first tile, then the window's.  t_begin, t_end and the loop below
@@ -606,7 +630,7 @@ __global__ void __launch_bounds__(kThreads) attention_decode_kernel(
             for (int i = 0; i < 4; ++i) {
                 const int key = key0 + n * 8 + tq * 2 + (i & 1);
                 const bool visible = key <= pos && (key >= first_key || key < window.keep);
-                s[n][i] = visible ? s[n][i] * scale_log2 : -INFINITY;
+                s[n][i] = visible ? score(s[n][i]) : -INFINITY;
             }
         uint32_t pf[1][4];
         softmax_tile<D, 2>(s, st, o, pf);
@@ -1561,7 +1585,7 @@ int launch_decode(void* out, float* part_o, float* part_ml, const void* q, const
     // pairs of 1,024 keys on: 4.38 against 4.76 ms per step at batch 24 with 4,096 keys).
     const bool second_pass = (long long)n_pairs > (long long)sm_count() * decode_blocks_per_sm<D, 2>();
     const bool asked_for = (hints & 2) != 0;
-    if (n_splits == 1 && n_pages > 0 && window.keep == 0 && window.chunk == 0 && !window.split_weights && (g_decode_stream == 2 || (g_decode_stream == 1 && (second_pass || asked_for)))) {
+    if (n_splits == 1 && n_pages > 0 && window.keep == 0 && window.chunk == 0 && !window.split_weights && !window.shape.active() && (g_decode_stream == 2 || (g_decode_stream == 1 && (second_pass || asked_for)))) {
         const int taken = g_decode_stream_stages >= 6
             ? launch_decode_stream<D, 6, FUSED>(out, q, row_slot, row_pos, kv, n_pages, n_seqs, n_q, scale, window, err,
                                                 stream, fused, hints)
@@ -1645,14 +1669,16 @@ THN_API int thn_attention_prefill_tile_rows() { return kPrefillRows; }
 // (window_size > 0) the first keep_first positions of a sequence stay visible as well; with
 // chunk > 0 (and no window) a row sees the keys of its own chunk of that many positions only.
 // split_weights: the softmax weights go to the tensor cores as two bfloat16 parts (KeyWindow).
+// softcap, temp_coef, temp_every: the ScoreShape of common.cuh (0: none).
 THN_API int thn_attention_prefill_bf16(void* out, const void* q, const int* tile_row0, const int* tile_rows,
                                        int n_tiles, const int* row_slot, const int* row_pos, const void* kv_base,
                                        const int* block_table, int bt_stride, int n_kv, int page_size, int head_dim,
                                        int n_q, float scale, int window_size, int keep_first, int chunk, int split_weights,
-                                       int* err, cudaStream_t stream) {
+                                       float softcap, float temp_coef, int temp_every, int* err, cudaStream_t stream) {
     THN_CHECK_ARG(n_tiles >= 0 && n_q > 0 && keep_first >= 0 && chunk >= 0, "attention_prefill: bad sizes");
     THN_CHECK_ARG(chunk == 0 || (window_size <= 0 && keep_first == 0), "attention_prefill: chunks stand instead of a window");
-    const KeyWindow window(window_size, keep_first, chunk, split_weights ? 1 : 0);
+    THN_CHECK_ARG(softcap >= 0.f && temp_every >= 0, "attention_prefill: a score cap and a temperature period are not negative");
+    const KeyWindow window(window_size, keep_first, chunk, split_weights ? 1 : 0, ScoreShape{softcap, temp_coef, temp_every});
     THN_UNSUPPORTED_IF(!thn_attention_mma_supported(head_dim, page_size, n_q, n_kv),
                        "attention_prefill: head_dim %d, page %d, heads %d/%d not supported by the tensor-core kernel",
                        head_dim, page_size, n_q, n_kv);
@@ -1731,12 +1757,14 @@ THN_API void thn_set_decode_stream(int mode, int stages) {
 THN_API int thn_attention_decode_bf16(void* out, const void* q, const int* row_slot, const int* row_pos,
                                       const void* kv_base, const int* block_table, int bt_stride, int n_kv,
                                       int page_size, int head_dim, int n_seqs, int n_q, int n_splits, float scale,
-                                      int window_size, int keep_first, int chunk, int split_weights, float* scratch,
+                                      int window_size, int keep_first, int chunk, int split_weights, float softcap,
+                                      float temp_coef, int temp_every, float* scratch,
                                       int* counters, long long n_pages, int hints, int* err, cudaStream_t stream) {
     THN_CHECK_ARG(n_seqs >= 0 && n_q > 0 && n_splits >= 1 && n_splits <= 65535 && keep_first >= 0 && chunk >= 0,
                   "attention_decode: bad sizes");
     THN_CHECK_ARG(chunk == 0 || (window_size <= 0 && keep_first == 0), "attention_decode: chunks stand instead of a window");
-    const KeyWindow window(window_size, keep_first, chunk, split_weights ? 1 : 0);
+    THN_CHECK_ARG(softcap >= 0.f && temp_every >= 0, "attention_decode: a score cap and a temperature period are not negative");
+    const KeyWindow window(window_size, keep_first, chunk, split_weights ? 1 : 0, ScoreShape{softcap, temp_coef, temp_every});
     THN_CHECK_ARG(counters == nullptr || n_splits <= 32, "attention_decode: at most 32 splits with counters, got %d",
                   n_splits);
     THN_UNSUPPORTED_IF(!thn_attention_mma_supported(head_dim, page_size, n_q, n_kv),
@@ -1850,7 +1878,8 @@ THN_API int thn_attention_decode_bf16_no_alloc(void* out, const void* q, const i
         if (scratch == nullptr) return THN_BAD_ARGUMENT;
     }
     return thn_attention_decode_bf16(out, q, row_slot, row_pos, kv_base, block_table, bt_stride, n_kv, page_size,
-                                     head_dim, n_seqs, n_q, n_splits, scale, window, /*keep_first=*/0, /*chunk=*/0, /*split_weights=*/0, scratch,
+                                     head_dim, n_seqs, n_q, n_splits, scale, window, /*keep_first=*/0, /*chunk=*/0, /*split_weights=*/0,
+                                     /*softcap=*/0.f, /*temp_coef=*/0.f, /*temp_every=*/0, scratch,
                                      nullptr, /*n_pages=*/0, /*hints=*/1, err,
                                      stream);
 }

@@ -209,7 +209,8 @@ __global__ void __launch_bounds__(kThreads, 2) attention_tcgen05_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
     __nv_bfloat16* __restrict__ out, const int* __restrict__ tile_row0, const int* __restrict__ tile_rows,
     const int* __restrict__ row_slot, const int* __restrict__ row_pos, const int* __restrict__ block_table,
-    int bt_stride, int n_kv, int n_q, float scale_log2, int window, int keep_first, int chunk, int* __restrict__ err) {
+    int bt_stride, int n_kv, int n_q, float scale_log2, int window, int keep_first, int chunk, ScoreShape shape,
+    int* __restrict__ err) {
     pdl_launch_dependents();
     pdl_wait();
     extern __shared__ __align__(1024) unsigned char smem_raw[];      // swizzled tiles want 1024-byte alignment
@@ -362,6 +363,12 @@ __global__ void __launch_bounds__(kThreads, 2) attention_tcgen05_kernel(
         const int r = quarter * 32 + lane;                   // row of the tile
         const int pos = pos0 + r;
         const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
+        // This row's scores on their way into the log2 domain: s * row_mul, or with a cap c
+        // c log2(e) tanh(s * cap_mul) (then row_mul is 1).
+        const float row_factor = scale_log2 * shape.row_factor(pos);
+        const float cap_mul = shape.cap > 0.f ? row_factor / (kLog2e * shape.cap) : 0.f;
+        const float cap_post = shape.cap * kLog2e;
+        const float row_mul = shape.cap > 0.f ? 1.0f : row_factor;
         float run_max = -INFINITY, run_sum = 0.f;
         bool ok = true;
         int it = 0;
@@ -388,6 +395,10 @@ __global__ void __launch_bounds__(kThreads, 2) attention_tcgen05_kernel(
             const bool whole = key0 + kKeys - 1 <= warp_first && (window <= 0 || key0 > warp_last - window) &&
                                (chunk <= 0 || key0 >= warp_last / chunk * chunk);
             const int chunk_start = chunk > 0 ? pos / chunk * chunk : 0;
+            if (shape.cap > 0.f) {
+#pragma unroll
+                for (int i = 0; i < 64; ++i) s[i] = cap_post * tanh_by_exp2(s[i] * cap_mul);
+            }
             if (!whole) {
 #pragma unroll
                 for (int i = 0; i < 64; ++i) {
@@ -398,7 +409,7 @@ __global__ void __launch_bounds__(kThreads, 2) attention_tcgen05_kernel(
             }
 #pragma unroll
             for (int i = 0; i < 64; i += 2) tile_max = fmaxf(tile_max, fmaxf(s[i], s[i + 1]));
-            tile_max *= scale_log2;                                        // scale > 0: the maximum scales with it
+            tile_max *= row_mul;                                           // a positive factor: the maximum scales with it
             // The reference point of the exponentials follows the maximum only when the maximum
             // has moved by more than 2^8 (softmax does not depend on the reference point; P stays
             // below 2^8, far inside bfloat16 and float32 range), so that the output accumulator
@@ -417,8 +428,8 @@ __global__ void __launch_bounds__(kThreads, 2) attention_tcgen05_kernel(
                 __nv_bfloat162* pb = reinterpret_cast<__nv_bfloat162*>(&packed[c]);
 #pragma unroll
                 for (int e = 0; e < 8; e += 2) {
-                    const float p0 = fast_exp2(fmaf(s[c * 8 + e], scale_log2, -base));
-                    const float p1 = fast_exp2(fmaf(s[c * 8 + e + 1], scale_log2, -base));
+                    const float p0 = fast_exp2(fmaf(s[c * 8 + e], row_mul, -base));
+                    const float p1 = fast_exp2(fmaf(s[c * 8 + e + 1], row_mul, -base));
                     sum += p0 + p1;
                     pb[e / 2] = __floats2bfloat162_rn(p0, p1);
                 }
@@ -545,14 +556,17 @@ THN_API int thn_attention_tcgen05_supported(int head_dim, int page_size, int n_q
 // Same contract as thn_attention_prefill_bf16 with row tiles of 128 rows (tile_rows 1..128);
 // n_rows_total is the number of packed rows of q and out, n_pages the pages of the cache entry.
 // With a window the first keep_first positions of a sequence stay visible as well; with chunk > 0
-// (and no window) a row sees the keys of its own chunk of that many positions only.
+// (and no window) a row sees the keys of its own chunk of that many positions only.  softcap,
+// temp_coef, temp_every: the ScoreShape of common.cuh (0: none).
 THN_API int thn_attention_prefill_tcgen05(void* out, const void* q, const int* tile_row0, const int* tile_rows,
                                           int n_tiles, int n_rows_total, const int* row_slot, const int* row_pos,
                                           const void* kv_base, long long n_pages, const int* block_table,
                                           int bt_stride, int n_kv, int page_size, int head_dim, int n_q, float scale,
-                                          int window, int keep_first, int chunk, int* err, cudaStream_t stream) {
+                                          int window, int keep_first, int chunk, float softcap, float temp_coef,
+                                          int temp_every, int* err, cudaStream_t stream) {
     THN_CHECK_ARG(n_tiles >= 0 && n_q > 0 && n_rows_total >= 0 && n_pages > 0 && keep_first >= 0 && chunk >= 0,
                   "attention_tcgen05: bad sizes");
+    THN_CHECK_ARG(softcap >= 0.f && temp_every >= 0, "attention_tcgen05: a score cap and a temperature period are not negative");
     THN_CHECK_ARG(chunk == 0 || window <= 0, "attention_tcgen05: chunks stand instead of a window");
     THN_UNSUPPORTED_IF(!thn_attention_tcgen05_supported(head_dim, page_size, n_q, n_kv),
                        "attention_tcgen05: head_dim %d, page %d, heads %d/%d not supported", head_dim, page_size, n_q,
@@ -581,6 +595,6 @@ THN_API int thn_attention_prefill_tcgen05(void* out, const void* q, const int* t
     dim3 grid(n_q, n_tiles);
     thn_launch(attention_tcgen05_kernel, grid, kThreads, kSmemBytes, stream, map_q, map_kv, (__nv_bfloat16*)out,
                tile_row0, tile_rows, row_slot, row_pos, block_table, bt_stride, n_kv, n_q, scale * kLog2e, window,
-               window > 0 ? keep_first : 0, chunk, err);
+               window > 0 ? keep_first : 0, chunk, ScoreShape{softcap, temp_coef, temp_every}, err);
     return thn_launch_status("attention_tcgen05");
 }

@@ -161,6 +161,32 @@ __device__ __forceinline__ float block_sum(float v, float* scratch /* >= 33 floa
     return scratch[32];
 }
 
+// How attention scores are shaped between q . k and the softmax, beyond the plain scale:
+//   temperature  the scores of the query at position p are multiplied by
+//                1 + temp_coef * ln(floor((p + 1) / temp_every) + 1)       (temp_every 0: none)
+//   cap          score <- cap * tanh(score / cap)                           (cap 0: none)
+// in this order, after the scale.  float32 throughout.
+struct ScoreShape {
+    float cap;
+    float temp_coef;
+    int temp_every;
+    __host__ __device__ bool active() const { return cap > 0.f || temp_every > 0; }
+    // the factor on the scores of the row at position pos
+    __device__ __forceinline__ float row_factor(int pos) const {
+        return temp_every > 0 ? 1.0f + temp_coef * logf((float)((pos + 1) / temp_every) + 1.0f) : 1.0f;
+    }
+    // the cap, with the library's tanh: for the kernels that compute a score at a time
+    __device__ __forceinline__ float capped(float s) const { return cap > 0.f ? cap * tanhf(s / cap) : s; }
+};
+
+// tanh from one exponential and one division, both of the fast kind: absolute error about
+// 2e-7 everywhere (it saturates to +-1 exactly), which is what the tensor-core attention
+// kernels need of a capped score.
+__device__ __forceinline__ float tanh_by_exp2(float x) {
+    const float e = exp2f(x * 2.8853900817779268f);      // e^(2x)
+    return 1.0f - __fdividef(2.0f, 1.0f + e);
+}
+
 // Geometry of one cache entry: pages of page_size tokens; inside a page K then V, each
 // [n_kv][page_size][head_dim] (V: [n_kv][page_size][value_dim] where values have a size of
 // their own; kernels that take such entries address them with kv_offset_sized).

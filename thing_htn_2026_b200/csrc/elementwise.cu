@@ -61,10 +61,14 @@ THN_API int thn_gather_rows(void* out, const void* table, const int* index, int 
 }
 
 // out[m] = float(table[index[m]]) * scale in float32: token embeddings that start a residual
-// stream kept in float32.
+// stream kept in float32.  With freq (double [ceil(width / 2)]) and row_pos a sinusoidal
+// position vector is added: entry 2i gets sin(p f_i), entry 2i + 1 cos(p f_i), p the row's
+// position.  The angle and its sine are computed in double and rounded once, so that a far
+// position is as exact as a near one.
 template <typename T>
 __global__ void gather_rows_scaled_kernel(float* __restrict__ out, const T* __restrict__ table,
                                           const int* __restrict__ index, int width, int n_table_rows, float scale,
+                                          const int* __restrict__ row_pos, const double* __restrict__ freq,
                                           int* __restrict__ err) {
     pdl_launch_dependents();
     pdl_wait();
@@ -76,23 +80,52 @@ __global__ void gather_rows_scaled_kernel(float* __restrict__ out, const T* __re
     }
     const T* src = table + (size_t)row * width;
     float* dst = out + (size_t)m * width;
-    for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = to_f32<T>(src[i]) * scale;
+    if (freq == nullptr) {
+        for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = to_f32<T>(src[i]) * scale;
+        return;
+    }
+    const double p = (double)row_pos[m];
+    for (int pair = threadIdx.x; 2 * pair < width; pair += blockDim.x) {
+        double sn, cs;
+        sincos(p * freq[pair], &sn, &cs);
+        dst[2 * pair] = to_f32<T>(src[2 * pair]) * scale + (float)sn;
+        if (2 * pair + 1 < width) dst[2 * pair + 1] = to_f32<T>(src[2 * pair + 1]) * scale + (float)cs;
+    }
 }
 
+// row_pos and freq: both or neither.
 THN_API int thn_gather_rows_scaled(float* out, const void* table, const int* index, int n_rows, int width,
-                                   int n_table_rows, float scale, int dtype, int* err, cudaStream_t stream) {
+                                   int n_table_rows, float scale, const int* row_pos, const double* freq, int dtype,
+                                   int* err, cudaStream_t stream) {
     THN_CHECK_ARG(n_rows >= 0 && width > 0 && n_table_rows > 0, "gather_rows_scaled: bad sizes rows=%d width=%d table=%d",
                   n_rows, width, n_table_rows);
+    THN_CHECK_ARG((row_pos == nullptr) == (freq == nullptr), "gather_rows_scaled: positions and frequencies go together");
     if (n_rows == 0) return THN_OK;
     if (dtype == THN_F32)
         thn_launch(gather_rows_scaled_kernel<float>, n_rows, 256, 0, stream, out, (const float*)table, index, width,
-                   n_table_rows, scale, err);
+                   n_table_rows, scale, row_pos, freq, err);
     else if (dtype == THN_BF16)
         thn_launch(gather_rows_scaled_kernel<__nv_bfloat16>, n_rows, 256, 0, stream, out, (const __nv_bfloat16*)table, index,
-                   width, n_table_rows, scale, err);
+                   width, n_table_rows, scale, row_pos, freq, err);
     else
         THN_CHECK_ARG(false, "gather_rows_scaled: unknown dtype %d", dtype);
     return thn_launch_status("gather_rows_scaled");
+}
+
+// x[i] *= scale in place, float32: a constant factor on logits.
+__global__ void scale_f32_kernel(float* __restrict__ x, long long n, float scale) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < n; e += stride) x[e] *= scale;
+}
+
+THN_API int thn_scale_f32(float* x, long long n, float scale, cudaStream_t stream) {
+    THN_CHECK_ARG(n >= 0, "scale_f32: bad size");
+    if (n == 0) return THN_OK;
+    const long long want = (n + 255) / 256;
+    thn_launch(scale_f32_kernel, (unsigned)(want < 148 * 16 ? want : 148 * 16), 256, 0, stream, x, n, scale);
+    return thn_launch_status("scale_f32");
 }
 
 // out[m, i] = a[m, i] * logistic(g[m, i]): an output gate on a mixer's concatenated heads.  The
@@ -452,6 +485,59 @@ THN_API int thn_clamped_glu(void* out, const void* gu, int rows, int inter, floa
     else
         THN_CHECK_ARG(false, "clamped_glu: unknown dtype %d", dtype);
     return thn_launch_status("clamped_glu");
+}
+
+// out = a N(z) + b N(z^2) + c N(z^3) + e per row, powers taken entry by entry and
+// N(v) = v / sqrt(mean(v^2) + eps) over the row; (a, b, c, e) = coef[0..3].  One block per row,
+// the row staged in shared memory; the three sums of squares are float32 and their order depends
+// on the block size only; one rounding at the store.
+template <typename T>
+__global__ void __launch_bounds__(256) polynorm_kernel(T* __restrict__ out, const T* __restrict__ z,
+                                                       const float* __restrict__ coef, int width, float eps) {
+    pdl_launch_dependents();
+    pdl_wait();
+    extern __shared__ float poly_row[];
+    __shared__ float scratch[33];
+    const size_t base = (size_t)blockIdx.x * width;
+    float s1 = 0.f, s2 = 0.f, s3 = 0.f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float v = to_f32<T>(z[base + i]);
+        poly_row[i] = v;
+        const float v2 = v * v;
+        s1 += v2;
+        s2 += v2 * v2;
+        s3 += v2 * v2 * v2;
+    }
+    const float n = (float)width;
+    const float r1 = coef[0] / sqrtf(block_sum(s1, scratch) / n + eps);
+    const float r2 = coef[1] / sqrtf(block_sum(s2, scratch) / n + eps);
+    const float r3 = coef[2] / sqrtf(block_sum(s3, scratch) / n + eps);
+    const float shift = coef[3];
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float v = poly_row[i];
+        out[base + i] = from_f32<T>(v * (r1 + v * (r2 + v * r3)) + shift);
+    }
+}
+
+// z, out [rows, width] of the activation type; coef float32 [4].
+THN_API int thn_polynorm(void* out, const void* z, const float* coef, int rows, int width, float eps, int dtype,
+                         cudaStream_t stream) {
+    THN_CHECK_ARG(rows >= 0 && width > 0 && eps > 0.f && coef != nullptr, "polynorm: bad sizes rows=%d width=%d", rows, width);
+    if (rows == 0) return THN_OK;
+    const size_t smem = (size_t)width * sizeof(float);
+    THN_UNSUPPORTED_IF(smem > 200 * 1024, "polynorm: rows of %d values do not fit shared memory", width);
+    if (dtype == THN_F32) {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(polynorm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        thn_launch(polynorm_kernel<float>, rows, 256, smem, stream, (float*)out, (const float*)z, coef, width, eps);
+    } else if (dtype == THN_BF16) {
+        if (smem > 48 * 1024)
+            cudaFuncSetAttribute(polynorm_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        thn_launch(polynorm_kernel<__nv_bfloat16>, rows, 256, smem, stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)z, coef,
+                   width, eps);
+    } else {
+        THN_CHECK_ARG(false, "polynorm: unknown dtype %d", dtype);
+    }
+    return thn_launch_status("polynorm");
 }
 
 // ------------------------------------------------------------------ step bookkeeping

@@ -1,6 +1,7 @@
 // Routing of a mixture of experts, and the experts' activation with the routing weights.
 //
-//   moe_route   per row: scores s = softmax(z) over all experts; the experts form `groups` equal
+//   moe_route   per row: scores s = softmax(z) over all experts (scoring 0) or s = logistic(z),
+//               each expert by itself (scoring 1); the experts form `groups` equal
 //               groups of neighbours, a group's score is its largest s, and only experts of the
 //               `keep` best groups can be chosen; the `top` allowed experts with the largest s
 //               are chosen (the lower index wins a tie); a chosen expert's weight is s * scale,
@@ -12,6 +13,14 @@
 //               0.5 u (1 + erf(u / sqrt 2)).  An expert that was not chosen gets zeros, so one
 //               down-projection over all columns gives the weighted sum of the chosen experts'
 //               outputs plus the gated shared expert's.
+//   routed_clamped_glu   experts of the form down(g * logistic(a g) * (u + 1)) with
+//               g = min(gate(x'), limit), u = clamp(up(x'), -limit, limit), whose input is the
+//               token times its routing weight, x' = w x.  The gate and up projections of all
+//               experts and of the shared expert are one product over x; a projection is linear,
+//               so the kernel multiplies the projected values by w (float32) before the clamps.
+//               A row holds [gates of all columns | ups of all columns]; the columns are
+//               [experts * ff | shared_ff].  The shared expert sees the token itself, has a limit
+//               of its own, and its columns are multiplied by logistic(gate logit of the row).
 #include <math.h>
 
 #include "common.cuh"
@@ -37,7 +46,7 @@ __device__ __forceinline__ Best warp_best(Best b) {
 
 __global__ void __launch_bounds__(kRouteWarps * 32) moe_route_kernel(
     float* __restrict__ dense, int* __restrict__ chosen, float* __restrict__ chosen_weight, const float* __restrict__ z,
-    long long z_stride, int n_rows, int n_experts, int n_groups, int keep, int top, float scale) {
+    long long z_stride, int n_rows, int n_experts, int n_groups, int keep, int top, float scale, int scoring) {
     pdl_launch_dependents();
     pdl_wait();
     extern __shared__ float shared[];     // per warp: scores [experts], group scores [groups]
@@ -49,19 +58,26 @@ __global__ void __launch_bounds__(kRouteWarps * 32) moe_route_kernel(
     const float* zr = z + (size_t)row * z_stride;
     const int per = n_experts / n_groups;
 
-    float mx = -INFINITY;
-    for (int e = lane; e < n_experts; e += 32) mx = fmaxf(mx, zr[e]);
-    mx = warp_max(mx);
-    float sum = 0.f;
-    for (int e = lane; e < n_experts; e += 32) {
-        const float v = expf(zr[e] - mx);
-        s[e] = v;
-        sum += v;
-    }
-    sum = warp_sum(sum);
-    for (int e = lane; e < n_experts; e += 32) {
-        s[e] = s[e] / sum;
-        dense[(size_t)row * n_experts + e] = 0.f;
+    if (scoring == 1) {
+        for (int e = lane; e < n_experts; e += 32) {
+            s[e] = 1.0f / (1.0f + expf(-zr[e]));
+            dense[(size_t)row * n_experts + e] = 0.f;
+        }
+    } else {
+        float mx = -INFINITY;
+        for (int e = lane; e < n_experts; e += 32) mx = fmaxf(mx, zr[e]);
+        mx = warp_max(mx);
+        float sum = 0.f;
+        for (int e = lane; e < n_experts; e += 32) {
+            const float v = expf(zr[e] - mx);
+            s[e] = v;
+            sum += v;
+        }
+        sum = warp_sum(sum);
+        for (int e = lane; e < n_experts; e += 32) {
+            s[e] = s[e] / sum;
+            dense[(size_t)row * n_experts + e] = 0.f;
+        }
     }
     __syncwarp();
     for (int g = lane; g < n_groups; g += 32) {
@@ -154,14 +170,78 @@ __global__ void routed_gelu_bf16_vec_kernel(__nv_bfloat16* __restrict__ out, con
     *reinterpret_cast<uint4*>(out + row * width + c) = packed;
 }
 
+// One thread per column of a row; see the head of the file.  A column of an expert that was not
+// chosen (weight 0) is not read.
+template <typename T>
+__global__ void routed_clamped_glu_kernel(T* __restrict__ out, const T* __restrict__ gu, const float* __restrict__ dense,
+                                          const float* __restrict__ shared_logit, long long logit_stride, long long n,
+                                          int width, int n_experts, int ff, float limit, float shared_limit, float alpha) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= n) return;
+    const long long row = e / width;
+    const int c = (int)(e - row * width);
+    float w = 1.0f, lim = shared_limit, after = 1.0f;
+    if (c < n_experts * ff) {
+        w = dense[row * n_experts + c / ff];
+        lim = limit;
+        if (w == 0.f) { out[e] = from_f32<T>(0.f); return; }
+    } else if (shared_logit) {
+        after = 1.0f / (1.0f + expf(-shared_logit[row * logit_stride]));
+    }
+    const T* src = gu + row * 2 * width;
+    const float g = fminf(w * to_f32<T>(src[c]), lim);
+    const float u = fminf(fmaxf(w * to_f32<T>(src[width + c]), -lim), lim);
+    out[e] = from_f32<T>(g / (1.0f + expf(-alpha * g)) * (u + 1.0f) * after);
+}
+
+// The same, eight bfloat16 columns per thread (16-byte accesses), one row per blockIdx.y: for
+// sizes where no group of eight columns straddles two experts.
+__global__ void routed_clamped_glu_bf16_vec_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ gu,
+                                                   const float* __restrict__ dense, const float* __restrict__ shared_logit,
+                                                   long long logit_stride, int width, int n_experts, int ff, float limit,
+                                                   float shared_limit, float alpha) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+    if (c >= width) return;
+    const long long row = blockIdx.y;
+    float w = 1.0f, lim = shared_limit, after = 1.0f;
+    if (c < n_experts * ff) {
+        w = dense[row * n_experts + c / ff];
+        lim = limit;
+    } else if (shared_logit) {
+        after = 1.0f / (1.0f + expf(-shared_logit[row * logit_stride]));
+    }
+    uint4 packed = make_uint4(0, 0, 0, 0);
+    if (w != 0.f) {
+        const uint4 gv = *reinterpret_cast<const uint4*>(gu + row * 2 * width + c);
+        const uint4 uv = *reinterpret_cast<const uint4*>(gu + row * 2 * width + width + c);
+        const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&gv);
+        const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&uv);
+        __nv_bfloat162* ob = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float2 g = __bfloat1622float2(g2[j]), u = __bfloat1622float2(u2[j]);
+            const float g0 = fminf(w * g.x, lim), g1 = fminf(w * g.y, lim);
+            const float u0 = fminf(fmaxf(w * u.x, -lim), lim), u1 = fminf(fmaxf(w * u.y, -lim), lim);
+            ob[j] = __floats2bfloat162_rn(g0 / (1.0f + expf(-alpha * g0)) * (u0 + 1.0f) * after,
+                                          g1 / (1.0f + expf(-alpha * g1)) * (u1 + 1.0f) * after);
+        }
+    }
+    *reinterpret_cast<uint4*>(out + row * width + c) = packed;
+}
+
 }  // namespace
 
 // z float32 [rows, >= experts] with rows z_stride apart; dense float32 [rows, experts]; chosen
 // int32 and chosen_weight float32 [rows, top].
 THN_API int thn_moe_route(float* dense, int* chosen, float* chosen_weight, const float* z, long long z_stride, int n_rows,
-                          int n_experts, int n_groups, int keep, int top, float scale, cudaStream_t stream) {
+                          int n_experts, int n_groups, int keep, int top, float scale, int scoring, cudaStream_t stream) {
     THN_CHECK_ARG(n_rows >= 0 && n_experts > 0 && n_groups > 0 && n_experts % n_groups == 0,
                   "moe_route: %d experts in %d groups", n_experts, n_groups);
+    THN_CHECK_ARG(scoring == 0 || scoring == 1, "moe_route: scoring %d (0: softmax, 1: logistic)", scoring);
     THN_CHECK_ARG(keep > 0 && keep <= n_groups && top > 0 && top <= keep * (n_experts / n_groups),
                   "moe_route: top %d of the experts of %d groups out of %d", top, keep, n_groups);
     THN_UNSUPPORTED_IF(n_experts > 4096, "moe_route: %d experts, at most 4096", n_experts);
@@ -170,7 +250,7 @@ THN_API int thn_moe_route(float* dense, int* chosen, float* chosen_weight, const
     if (smem > 48 * 1024)
         cudaFuncSetAttribute(moe_route_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     thn_launch(moe_route_kernel, (n_rows + kRouteWarps - 1) / kRouteWarps, kRouteWarps * 32, smem, stream, dense, chosen,
-               chosen_weight, z, z_stride, n_rows, n_experts, n_groups, keep, top, scale);
+               chosen_weight, z, z_stride, n_rows, n_experts, n_groups, keep, top, scale, scoring);
     return thn_launch_status("moe_route");
 }
 
@@ -199,4 +279,37 @@ THN_API int thn_routed_gelu(void* out, const void* u, const float* dense, const 
     else
         THN_CHECK_ARG(false, "routed_gelu: unknown dtype %d", dtype);
     return thn_launch_status("routed_gelu");
+}
+
+// gu [rows, 2 * (experts * ff + shared_ff)] of the activation type: the gates of all columns, then
+// the ups; out [rows, experts * ff + shared_ff]; dense float32 [rows, experts]; shared_logit: the
+// rows' gate logits of the shared expert, logit_stride apart (null: no gate).
+THN_API int thn_routed_clamped_glu(void* out, const void* gu, const float* dense, const float* shared_logit,
+                                   long long logit_stride, int n_rows, int n_experts, int ff, int shared_ff, float limit,
+                                   float shared_limit, float alpha, int dtype, cudaStream_t stream) {
+    THN_CHECK_ARG(n_rows >= 0 && n_experts >= 0 && ff >= 0 && shared_ff >= 0 && n_experts * ff + shared_ff > 0,
+                  "routed_clamped_glu: bad sizes");
+    THN_CHECK_ARG((n_experts * ff == 0 || limit > 0.f) && (shared_ff == 0 || shared_limit > 0.f),
+                  "routed_clamped_glu: limits must be positive");
+    const int width = n_experts * ff + shared_ff;
+    const long long n = (long long)n_rows * width;
+    if (n == 0) return THN_OK;
+    const unsigned blocks = (unsigned)((n + 255) / 256);
+    if (dtype == THN_BF16 && ff % 8 == 0 && width % 8 == 0 && n_rows <= 65535 &&
+        ((((uintptr_t)out) | ((uintptr_t)gu)) & 15) == 0) {
+        thn_launch(routed_clamped_glu_bf16_vec_kernel, dim3((width / 8 + 127) / 128, n_rows), 128, 0, stream,
+                   (__nv_bfloat16*)out, (const __nv_bfloat16*)gu, dense, shared_logit, logit_stride, width, n_experts, ff,
+                   limit, shared_limit, alpha);
+        return thn_launch_status("routed_clamped_glu");
+    }
+    if (dtype == THN_F32)
+        thn_launch(routed_clamped_glu_kernel<float>, blocks, 256, 0, stream, (float*)out, (const float*)gu, dense,
+                   shared_logit, logit_stride, n, width, n_experts, ff, limit, shared_limit, alpha);
+    else if (dtype == THN_BF16)
+        thn_launch(routed_clamped_glu_kernel<__nv_bfloat16>, blocks, 256, 0, stream, (__nv_bfloat16*)out,
+                   (const __nv_bfloat16*)gu, dense, shared_logit, logit_stride, n, width, n_experts, ff, limit, shared_limit,
+                   alpha);
+    else
+        THN_CHECK_ARG(false, "routed_clamped_glu: unknown dtype %d", dtype);
+    return thn_launch_status("routed_clamped_glu");
 }

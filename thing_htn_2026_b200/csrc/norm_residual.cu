@@ -1,12 +1,16 @@
 // Norms around a residual stream that is kept in float32 whatever the activation type is,
 // with an optional norm of the branch output before it is added:
 //
-//     h <- h + B(d),   B(d) = d                                                  (post kind 0)
+//     h <- h + m B(d + d2)   (d2, a second branch output, may be absent; m is 1 unless given)
+//                      B(d) = d                                                  (post kind 0)
 //                      B(d) = d / sqrt(mean(d^2) + eps_b) * (o_b + w_b)          (post kind 1, RMS)
 //                      B(d) = (d - mean d) / sqrt(var d + eps_b) * (o_b + w_b) + b_b   (post kind 2, layer norm)
 //     y  = N(h) with N of kind 1 or 2 as above (gain w, bias b), or
 //     y  = h rounded to the activation type (kind 3: the stream itself is what a sublayer reads), or
 //     no y (kind 0).
+//
+// An RMS norm of the stream (kind 1) may work in `groups` equal consecutive parts of the row,
+// each divided by its own sqrt(mean(part^2) + eps) before the gain over the whole row.
 //
 // o_b and o are gain offsets: 0 for a gain stored as it multiplies, 1 for a gain stored around
 // zero; a bias may be absent.  The variance is the mean of the squared deviations from the mean
@@ -25,7 +29,21 @@ struct NormArgs {
     float offset;
     float eps;
     int kind;     // 0 none, 1 RMS, 2 layer norm, 3 (output only) the stream as it is
+    int groups;   // kind 1 as an output: equal consecutive parts with statistics of their own (1: the whole row)
 };
+
+// 1 / sqrt(mean(part^2) + eps) of each of `groups` equal parts of the staged row, into rstd[];
+// a warp takes a part at a time, so the order of additions depends on the sizes only.
+__device__ __forceinline__ void group_statistics(const float* row, int width, int groups, float eps, float* rstd) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, per = width / groups;
+    for (int g = warp; g < groups; g += kThreads / 32) {
+        float ss = 0.f;
+        for (int i = lane; i < per; i += 32) ss += row[g * per + i] * row[g * per + i];
+        ss = warp_sum(ss);
+        if (lane == 0) rstd[g] = 1.0f / sqrtf(ss / (float)per + eps);
+    }
+    __syncthreads();
+}
 
 // (mean, 1 / sqrt(var + eps)) of the staged row for a norm of the given kind; mean is 0 for RMS.
 __device__ __forceinline__ float2 row_statistics(const float* row, int width, int kind, float eps, float* scratch) {
@@ -46,15 +64,16 @@ __device__ __forceinline__ float2 row_statistics(const float* row, int width, in
 
 template <typename T>
 __global__ void __launch_bounds__(kThreads) residual_norm_kernel(
-    T* __restrict__ y, float* __restrict__ h, const T* __restrict__ d, NormArgs post, NormArgs out, int width,
-    int h_is_new) {
+    T* __restrict__ y, float* __restrict__ h, const T* __restrict__ d, const T* __restrict__ d2, float mult,
+    NormArgs post, NormArgs out, int width, int h_is_new) {
     pdl_launch_dependents();
     pdl_wait();
     extern __shared__ float row[];
     __shared__ float scratch[33];
     const size_t base = (size_t)blockIdx.x * width;
     if (d) {
-        for (int i = threadIdx.x; i < width; i += kThreads) row[i] = to_f32<T>(d[base + i]);
+        for (int i = threadIdx.x; i < width; i += kThreads)
+            row[i] = d2 ? to_f32<T>(d[base + i]) + to_f32<T>(d2[base + i]) : to_f32<T>(d[base + i]);
         float2 st = make_float2(0.f, 1.f);
         if (post.kind) {
             __syncthreads();
@@ -66,6 +85,7 @@ __global__ void __launch_bounds__(kThreads) residual_norm_kernel(
                 v = (v - st.x) * st.y * (post.offset + post.gain[i]);
                 if (post.bias) v += post.bias[i];
             }
+            v *= mult;
             if (!h_is_new) v = h[base + i] + v;
             h[base + i] = v;
             row[i] = v;
@@ -79,6 +99,17 @@ __global__ void __launch_bounds__(kThreads) residual_norm_kernel(
         return;
     }
     __syncthreads();
+    if (out.kind == 1 && out.groups > 1) {
+        float* rstd = row + width;
+        group_statistics(row, width, out.groups, out.eps, rstd);
+        const int per = width / out.groups;
+        for (int i = threadIdx.x; i < width; i += kThreads) {
+            float v = row[i] * rstd[i / per] * (out.offset + out.gain[i]);
+            if (out.bias) v += out.bias[i];
+            y[base + i] = from_f32<T>(v);
+        }
+        return;
+    }
     const float2 st = row_statistics(row, width, out.kind, out.eps, scratch);
     for (int i = threadIdx.x; i < width; i += kThreads) {
         float v = (row[i] - st.x) * st.y * (out.offset + out.gain[i]);
@@ -88,14 +119,14 @@ __global__ void __launch_bounds__(kThreads) residual_norm_kernel(
 }
 
 template <typename T>
-int launch(void* y, float* h, const void* d, NormArgs post, NormArgs out, int rows, int width, int h_is_new,
-           cudaStream_t stream) {
-    const size_t smem = (size_t)width * sizeof(float);
+int launch(void* y, float* h, const void* d, const void* d2, float mult, NormArgs post, NormArgs out, int rows, int width,
+           int h_is_new, cudaStream_t stream) {
+    const size_t smem = (size_t)(width + (out.groups > 1 ? out.groups : 0)) * sizeof(float);
     if (smem > 48 * 1024) {
         THN_UNSUPPORTED_IF(smem > 200 * 1024, "residual_norm: rows of %d values do not fit shared memory", width);
         cudaFuncSetAttribute(residual_norm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     }
-    thn_launch(residual_norm_kernel<T>, rows, kThreads, smem, stream, (T*)y, h, (const T*)d, post, out, width, h_is_new);
+    thn_launch(residual_norm_kernel<T>, rows, kThreads, smem, stream, (T*)y, h, (const T*)d, (const T*)d2, mult, post, out, width, h_is_new);
     return thn_launch_status("residual_norm");
 }
 
@@ -171,11 +202,17 @@ __global__ void gated_head_norm_bf16_vec_kernel(__nv_bfloat16* __restrict__ out,
 // h float32 [rows, width], updated in place when d is given (h_is_new: h is not read, it
 // becomes B(d)); d and y of the activation type; gains and biases float32 [width] (a bias may
 // be null).  post_kind 0: d is added as it is; kind 0: no y is written; kind 3: y is h rounded.
-THN_API int thn_residual_norm(void* y, float* h, const void* d, const float* post_gain, const float* post_bias,
-                              float post_offset, float post_eps, int post_kind, const float* gain, const float* bias,
-                              float offset, float eps, int kind, int rows, int width, int h_is_new, int dtype,
-                              cudaStream_t stream) {
+// d2 (may be null): a second branch output, added to d before anything else; mult: the factor on
+// what is added to h; groups (kind 1 only, a divisor of width): parts of the row with statistics
+// of their own.
+THN_API int thn_residual_norm(void* y, float* h, const void* d, const void* d2, float mult, const float* post_gain,
+                              const float* post_bias, float post_offset, float post_eps, int post_kind, const float* gain,
+                              const float* bias, float offset, float eps, int kind, int groups, int rows, int width,
+                              int h_is_new, int dtype, cudaStream_t stream) {
     THN_CHECK_ARG(rows >= 0 && width > 0, "residual_norm: bad sizes rows=%d width=%d", rows, width);
+    THN_CHECK_ARG(d2 == nullptr || d != nullptr, "residual_norm: a second branch without a first");
+    THN_CHECK_ARG(groups >= 1 && width % groups == 0 && (groups == 1 || kind == 1),
+                  "residual_norm: %d groups over rows of %d (an RMS norm of the stream only)", groups, width);
     THN_CHECK_ARG(post_kind >= 0 && post_kind <= 2 && kind >= 0 && kind <= 3, "residual_norm: norm kinds %d, %d", post_kind,
                   kind);
     THN_CHECK_ARG(h != nullptr && (d != nullptr || kind != 0), "residual_norm: nothing to do");
@@ -184,10 +221,10 @@ THN_API int thn_residual_norm(void* y, float* h, const void* d, const float* pos
     THN_CHECK_ARG(!(kind == 1 || kind == 2) || (gain != nullptr && eps > 0.f), "residual_norm: gain missing, or eps <= 0");
     THN_CHECK_ARG(post_kind == 0 || (post_gain != nullptr && post_eps > 0.f), "residual_norm: post gain missing, or eps <= 0");
     if (rows == 0) return THN_OK;
-    const NormArgs post{post_gain, post_bias, post_offset, post_eps, d ? post_kind : 0};
-    const NormArgs out{gain, bias, offset, eps, kind};
-    if (dtype == THN_F32) return launch<float>(y, h, d, post, out, rows, width, h_is_new, stream);
-    if (dtype == THN_BF16) return launch<__nv_bfloat16>(y, h, d, post, out, rows, width, h_is_new, stream);
+    const NormArgs post{post_gain, post_bias, post_offset, post_eps, d ? post_kind : 0, 1};
+    const NormArgs out{gain, bias, offset, eps, kind, groups};
+    if (dtype == THN_F32) return launch<float>(y, h, d, d2, mult, post, out, rows, width, h_is_new, stream);
+    if (dtype == THN_BF16) return launch<__nv_bfloat16>(y, h, d, d2, mult, post, out, rows, width, h_is_new, stream);
     THN_CHECK_ARG(false, "residual_norm: unknown dtype %d", dtype);
     return THN_OK;
 }

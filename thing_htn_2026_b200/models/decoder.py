@@ -87,7 +87,7 @@ class DecoderModel:
     def hidden(self, tokens: torch.Tensor, ctx: StepContext):
         """All scheduled layers over the step's rows; returns the residual stream and the
         last branch output that has not been added yet."""
-        h = self.embedding.forward(tokens, ctx.err)
+        h = self.embedding.forward(tokens, ctx.err, ctx.rows)
         d: Optional[torch.Tensor] = None
         for entry in self.plan.schedule:
             h, d = self.layers[entry.layer].forward(h, d, ctx, entry)
@@ -98,6 +98,14 @@ class DecoderModel:
         """Final norm and head at the given rows (int32 indices; None: every row): float32.
         ``err``: the step's device error word."""
         post = None
+        if isinstance(d, Branch) and (d.second is not None or d.factor != 1.0):
+            # two sublayers side by side, or a factor on the add: the norm takes the branch whole
+            post = d.norm
+            if rows is not None:
+                d = Branch(ops.gather_rows(d.tensor, rows), d.norm,
+                           ops.gather_rows(d.second, rows) if d.second is not None else None, d.factor)
+                h = ops.gather_rows(h, rows)
+            return self.head.forward(self.final_norm.add_forward(h, d, post=post), err)
         if isinstance(d, Branch):        # a branch that passes a norm of its own before the add
             d, post = d.tensor, d.norm
         if rows is not None:

@@ -55,12 +55,18 @@ _SIGNATURES = {
                                         c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_longlong, c_int,
                                         c_void_p, c_void_p],
     "thn_attention_generic": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
-                              c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
-    "thn_residual_norm": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_float, c_int, c_void_p, c_void_p,
-                          c_float, c_float, c_int, c_int, c_int, c_int, c_int, c_void_p],
+                              c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_int, c_float, c_float, c_int,
+                              c_int, c_void_p, c_void_p],
+    "thn_residual_norm": [c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_float, c_float, c_int,
+                          c_void_p, c_void_p, c_float, c_float, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "thn_gated_head_norm": [c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_float, c_int, c_int, c_int, c_int,
                             c_int, c_int, c_void_p],
-    "thn_gather_rows_scaled": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p],
+    "thn_gather_rows_scaled": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_int,
+                               c_void_p, c_void_p],
+    "thn_scale_f32": [c_void_p, c_longlong, c_float, c_void_p],
+    "thn_polynorm": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p],
+    "thn_routed_clamped_glu": [c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_float,
+                               c_float, c_float, c_int, c_void_p],
     "thn_logistic_gate": [c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_void_p],
     "thn_latent_norm": [c_void_p, c_void_p, c_longlong, c_void_p, c_float, c_int, c_int, c_int, c_void_p],
     "thn_latent_assemble": [c_void_p, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int,
@@ -71,7 +77,7 @@ _SIGNATURES = {
     "thn_mlstm_recurrence": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_float, c_int,
                              c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_void_p],
     "thn_moe_route": [c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int, c_float,
-                      c_void_p],
+                      c_int, c_void_p],
     "thn_routed_gelu": [c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "thn_clamped_glu": [c_void_p, c_void_p, c_int, c_int, c_float, c_float, c_int, c_void_p],
     "thn_qk_prepare": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_float, c_float, c_void_p, c_void_p,
@@ -95,10 +101,10 @@ _SIGNATURES = {
     "thn_attention_fused_supported": [c_int, c_int, c_int, c_int],
     "thn_attention_prefill_bf16": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                                    c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_int,
-                                   c_void_p, c_void_p],
+                                   c_float, c_float, c_int, c_void_p, c_void_p],
     "thn_attention_decode_bf16": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
-                                  c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
-                                  c_longlong, c_int, c_void_p, c_void_p],
+                                  c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_int, c_float, c_float,
+                                  c_int, c_void_p, c_void_p, c_longlong, c_int, c_void_p, c_void_p],
     "thn_attention_decode_blocks_per_sm": [c_int],
     "thn_attention_decode_cluster_splits": [],
     "thn_attention_decode_one_wave_splits": [c_int, c_int, c_int],
@@ -109,7 +115,7 @@ _SIGNATURES = {
     "thn_attention_tcgen05_test_skip_loads": [c_int],
     "thn_attention_prefill_tcgen05": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p,
                                       c_void_p, c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
-                                      c_int, c_int, c_int, c_void_p, c_void_p],
+                                      c_int, c_int, c_int, c_float, c_float, c_int, c_void_p, c_void_p],
 }
 
 _lib = None
@@ -293,13 +299,45 @@ def gather_rows(table: torch.Tensor, index: torch.Tensor, err: Optional[torch.Te
 
 
 def gather_rows_scaled(table: torch.Tensor, index: torch.Tensor, scale: float,
-                       err: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """out[m] = float32(table[index[m]]) * scale: rows that start a residual stream kept in float32."""
+                       err: Optional[torch.Tensor] = None, row_pos: Optional[torch.Tensor] = None,
+                       frequencies: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[m] = float32(table[index[m]]) * scale: rows that start a residual stream kept in float32.
+    With ``frequencies`` (float64 [ceil(width / 2)]) and ``row_pos`` (int32 [rows]) a sinusoidal
+    position vector is added: ``sin(p f_i)`` at entry 2i and ``cos(p f_i)`` at entry 2i + 1."""
     _need(table, "gather_rows_scaled table")
     _need(index, "gather_rows_scaled index", torch.int32)
+    if (row_pos is None) != (frequencies is None):
+        raise KernelError("gather_rows_scaled: positions and frequencies go together")
+    if frequencies is not None:
+        _need(frequencies, "gather_rows_scaled frequencies", torch.float64)
+        _need(row_pos, "gather_rows_scaled positions", torch.int32)
+        if frequencies.shape[0] != (table.shape[1] + 1) // 2 or row_pos.shape[0] != index.shape[0]:
+            raise KernelError(f"gather_rows_scaled: {frequencies.shape[0]} frequencies for rows of {table.shape[1]}, "
+                              f"{row_pos.shape[0]} positions for {index.shape[0]} rows")
     out = torch.empty((index.shape[0], table.shape[1]), dtype=torch.float32, device=table.device)
     _call("thn_gather_rows_scaled", _ptr(out), _ptr(table), _ptr(index), index.shape[0], table.shape[1], table.shape[0],
-          float(scale), _code(table, "gather_rows_scaled"), _ptr(err), _stream())
+          float(scale), _ptr(row_pos), _ptr(frequencies), _code(table, "gather_rows_scaled"), _ptr(err), _stream())
+    return out
+
+
+def scale_(x: torch.Tensor, scale: float) -> torch.Tensor:
+    """x *= scale in place (float32): a constant factor on logits."""
+    _need(x, "scale_", torch.float32)
+    if scale != 1.0:
+        _call("thn_scale_f32", _ptr(x), x.numel(), float(scale), _stream())
+    return x
+
+
+def polynorm(z: torch.Tensor, coefficients: torch.Tensor, eps: float) -> torch.Tensor:
+    """z [rows, width] -> ``a N(z) + b N(z^2) + c N(z^3) + e`` with powers taken entry by entry,
+    ``N(v) = v / sqrt(mean(v^2) + eps)`` over a row and ``(a, b, c, e) = coefficients`` (float32 [4])."""
+    _need(z, "polynorm z")
+    _need(coefficients, "polynorm coefficients", torch.float32)
+    if z.dim() != 2 or coefficients.numel() != 4:
+        raise KernelError(f"polynorm: shapes z {tuple(z.shape)}, coefficients {tuple(coefficients.shape)}")
+    out = torch.empty_like(z)
+    _call("thn_polynorm", _ptr(out), _ptr(z), _ptr(coefficients), z.shape[0], z.shape[1], float(eps), _code(z, "polynorm"),
+          _stream())
     return out
 
 
@@ -383,20 +421,31 @@ class Gain:
     eps: float
     bias: Optional[torch.Tensor] = None
     kind: str = "rms"
+    groups: int = 1     # "rms" as the norm of the stream: equal consecutive parts with statistics of their own
 
 
 STREAM_AS_IS = Gain(None, 0.0, 1.0, None, "as_is")
 
 
 def residual_norm(h: Optional[torch.Tensor], d: Optional[torch.Tensor], post: Optional[Gain], gain: Optional[Gain],
-                  dtype: torch.dtype) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+                  dtype: torch.dtype, d2: Optional[torch.Tensor] = None,
+                  mult: float = 1.0) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
     """Norms around a residual stream ``h`` kept in float32 beside activations of ``dtype``:
-    ``h <- h + post(d)`` in place (``post`` None: ``d`` is added as it is; ``h`` None: the
-    stream starts as ``post(d)``), then ``y = gain(h)`` of ``dtype`` (``gain`` None: no y;
-    ``STREAM_AS_IS``: y is h rounded).  See :class:`Gain` for the norms.  Returns ``(h, y)``."""
+    ``h <- h + mult * post(d + d2)`` in place (``post`` None: the branch is added as it is; ``d2``
+    None: one branch; ``h`` None: the stream starts as that), then ``y = gain(h)`` of ``dtype``
+    (``gain`` None: no y; ``STREAM_AS_IS``: y is h rounded).  See :class:`Gain` for the norms.
+    Returns ``(h, y)``."""
     if d is None and h is None:
         raise KernelError("residual_norm: neither a stream nor a branch")
     h_is_new = h is None
+    if d2 is not None:
+        if d is None or tuple(d2.shape) != tuple(d.shape):
+            raise KernelError("residual_norm: a second branch goes with a first of its shape")
+        _need(d2, "residual_norm d2", dtype)
+    if gain is not None and gain.groups != 1 and (gain.kind != "rms" or h is not None and h.shape[-1] % gain.groups):
+        raise KernelError(f"residual_norm: {gain.groups} groups need an RMS norm over rows they divide")
+    if post is not None and post.groups != 1:
+        raise KernelError("residual_norm: the norm of a branch has no groups")
     if d is not None:
         _need(d, "residual_norm d", dtype)
     if h_is_new:
@@ -415,11 +464,11 @@ def residual_norm(h: Optional[torch.Tensor], d: Optional[torch.Tensor], post: Op
                 if t.shape[0] != width:
                     raise KernelError(f"residual_norm: {what} {name} has {t.shape[0]} entries, rows have {width}")
     y = torch.empty(h.shape, dtype=dtype, device=h.device) if gain is not None else None
-    _call("thn_residual_norm", _ptr(y), _ptr(h), _ptr(d), _ptr(post.weight) if post else None,
+    _call("thn_residual_norm", _ptr(y), _ptr(h), _ptr(d), _ptr(d2), float(mult), _ptr(post.weight) if post else None,
           _ptr(post.bias) if post else None, float(post.offset) if post else 0.0, float(post.eps) if post else 1.0,
           NORM_KINDS[post.kind] if post else 0, _ptr(gain.weight) if gain else None, _ptr(gain.bias) if gain else None,
           float(gain.offset) if gain else 0.0, float(gain.eps) if gain else 1.0, NORM_KINDS[gain.kind] if gain else 0,
-          rows, width, int(h_is_new), DTYPE_CODE[dtype], _stream())
+          int(gain.groups) if gain else 1, rows, width, int(h_is_new), DTYPE_CODE[dtype], _stream())
     return h, y
 
 
@@ -614,6 +663,28 @@ class KVView:
         return self.head_dim if self.value_dim is None else self.value_dim
 
 
+@dataclass(frozen=True)
+class ScoreShape:
+    """What happens to an attention score between the scale and the softmax.  ``temp_every`` > 0:
+    the scores of the query at position p are multiplied by
+    ``1 + temp_coef * ln(floor((p + 1) / temp_every) + 1)``.  ``softcap`` > 0: a score s becomes
+    ``softcap * tanh(s / softcap)``.  In this order; zeros: neither."""
+
+    softcap: float = 0.0
+    temp_coef: float = 0.0
+    temp_every: int = 0
+
+    @property
+    def active(self) -> bool:
+        return self.softcap > 0.0 or self.temp_every > 0
+
+    def args(self):
+        return float(self.softcap), float(self.temp_coef), int(self.temp_every)
+
+
+PLAIN_SCORES = ScoreShape()
+
+
 @dataclass
 class RowTiles:
     """Tiles of at most ``size`` consecutive rows of one sequence, for the prompt attention
@@ -671,7 +742,7 @@ def qk_norm_rope_cache(qkv, q_gain: Optional[torch.Tensor], k_gain: Optional[tor
 
 def attention_generic(q: torch.Tensor, rows: StepRows, kv: KVView, n_q: int, scale: float,
                       window: Optional[int], err: torch.Tensor, keep_first: int = 0, chunk: Optional[int] = None,
-                      exact_weights: bool = False) -> torch.Tensor:
+                      exact_weights: bool = False, shape: ScoreShape = PLAIN_SCORES) -> torch.Tensor:
     """One warp per (row, head), any sizes.  ``chunk``: a row sees only the keys of its own chunk
     of that many positions; ``exact_weights``: the softmax weights stay float32 where they
     multiply the values; the output has ``kv.v_dim`` entries per head."""
@@ -679,7 +750,7 @@ def attention_generic(q: torch.Tensor, rows: StepRows, kv: KVView, n_q: int, sca
     out = torch.empty((q.shape[0], n_q * kv.v_dim), dtype=q.dtype, device=q.device)
     _call("thn_attention_generic", _ptr(out), _ptr(q), _ptr(rows.row_slot), _ptr(rows.row_pos), _ptr(kv.storage),
           _ptr(kv.block_table), kv.block_table.shape[1], kv.n_kv, kv.page_size, kv.head_dim, kv.v_dim, rows.n_rows, n_q,
-          float(scale), int(window or 0), int(keep_first or 0), int(chunk or 0), int(bool(exact_weights)),
+          float(scale), int(window or 0), int(keep_first or 0), int(chunk or 0), int(bool(exact_weights)), *shape.args(),
           _code(q, "attention"), _ptr(err), _stream())
     return out
 
@@ -735,7 +806,8 @@ def prompt_attention_tile(dtype: torch.dtype, kv_head_dim: int, page_size: int, 
 
 def attention(q: torch.Tensor, rows: StepRows, kv: KVView, n_q: int, scale: float, window: Optional[int],
               err: torch.Tensor, tiles: Optional[RowTiles] = None, keep_first: int = 0,
-              chunk: Optional[int] = None, exact_weights: bool = False) -> torch.Tensor:
+              chunk: Optional[int] = None, exact_weights: bool = False,
+              shape: ScoreShape = PLAIN_SCORES) -> torch.Tensor:
     """Causal attention of the step's rows over the cache (which already holds the step's
     own keys).  Chooses the kernel by dtype, head size and step shape; the tensor-core
     kernels for steps of several tokens per sequence need ``tiles``.  With a window,
@@ -746,24 +818,26 @@ def attention(q: torch.Tensor, rows: StepRows, kv: KVView, n_q: int, scale: floa
     rounding and what the rounding left) in the ``mma.sync`` kernels.  The tcgen05 prompt kernel
     (head size 128) has one bfloat16 part only and is taken all the same: it is 2.4 to 3.6 times
     faster there than the ``mma.sync`` kernel with two parts; ``THN_ATTN_TCGEN05=0`` sends those
-    prompts to the latter."""
+    prompts to the latter.  ``shape``: a position-dependent factor on a row's scores and a tanh
+    cap (:class:`ScoreShape`), taken by every kernel but the streaming decode kernel."""
     keep_first = int(keep_first or 0) if window else 0
     if kv.v_dim != kv.head_dim:
-        return attention_generic(q, rows, kv, n_q, scale, window, err, keep_first, chunk, exact_weights)
+        return attention_generic(q, rows, kv, n_q, scale, window, err, keep_first, chunk, exact_weights, shape)
     if q.dtype == torch.bfloat16 and lib().thn_attention_mma_supported(kv.head_dim, kv.page_size, n_q, kv.n_kv):
         if rows.max_q_len == 1:
             return attention_decode_bf16(q, rows, kv, n_q, scale, window, err, keep_first=keep_first, chunk=chunk,
-                                         split_weights=exact_weights)
+                                         split_weights=exact_weights, shape=shape)
         if tiles is not None:
             if USE_TCGEN05_ATTENTION and lib().thn_attention_tcgen05_supported(kv.head_dim, kv.page_size, n_q, kv.n_kv):
-                return attention_prefill_tcgen05(q, rows, tiles, kv, n_q, scale, window, err, keep_first, chunk)
-            return attention_prefill_bf16(q, rows, tiles, kv, n_q, scale, window, err, keep_first, chunk, exact_weights)
-    return attention_generic(q, rows, kv, n_q, scale, window, err, keep_first, chunk, exact_weights)
+                return attention_prefill_tcgen05(q, rows, tiles, kv, n_q, scale, window, err, keep_first, chunk, shape)
+            return attention_prefill_bf16(q, rows, tiles, kv, n_q, scale, window, err, keep_first, chunk, exact_weights,
+                                          shape)
+    return attention_generic(q, rows, kv, n_q, scale, window, err, keep_first, chunk, exact_weights, shape)
 
 
 def attention_prefill_tcgen05(q: torch.Tensor, rows: StepRows, tiles: RowTiles, kv: KVView, n_q: int, scale: float,
                               window: Optional[int], err: torch.Tensor, keep_first: int = 0,
-                              chunk: Optional[int] = None) -> torch.Tensor:
+                              chunk: Optional[int] = None, shape: ScoreShape = PLAIN_SCORES) -> torch.Tensor:
     """tcgen05 / TMEM / TMA flash attention for steps with several tokens per sequence
     (bfloat16, head size 128)."""
     _need(q, "attention q", torch.bfloat16)
@@ -772,7 +846,7 @@ def attention_prefill_tcgen05(q: torch.Tensor, rows: StepRows, tiles: RowTiles, 
     _call("thn_attention_prefill_tcgen05", _ptr(out), _ptr(q), _ptr(tiles.row0), _ptr(tiles.rows),
           tiles.n, q.shape[0], _ptr(rows.row_slot), _ptr(rows.row_pos), _ptr(kv.storage), kv.storage.shape[0],
           _ptr(kv.block_table), kv.block_table.shape[1], kv.n_kv, kv.page_size, kv.head_dim, n_q, float(scale),
-          int(window or 0), int(keep_first or 0), int(chunk or 0), _ptr(err), _stream())
+          int(window or 0), int(keep_first or 0), int(chunk or 0), *shape.args(), _ptr(err), _stream())
     return out
 
 
@@ -793,7 +867,8 @@ def _check_tiles(tiles: RowTiles) -> None:
 
 def attention_prefill_bf16(q: torch.Tensor, rows: StepRows, tiles: RowTiles, kv: KVView, n_q: int, scale: float,
                            window: Optional[int], err: torch.Tensor, keep_first: int = 0,
-                           chunk: Optional[int] = None, split_weights: bool = False) -> torch.Tensor:
+                           chunk: Optional[int] = None, split_weights: bool = False,
+                           shape: ScoreShape = PLAIN_SCORES) -> torch.Tensor:
     """Tensor-core flash attention for steps with several tokens per sequence.  ``split_weights``:
     the softmax weights multiply the values as two bfloat16 parts (two products), not one."""
     _need(q, "attention q", torch.bfloat16)
@@ -802,7 +877,7 @@ def attention_prefill_bf16(q: torch.Tensor, rows: StepRows, tiles: RowTiles, kv:
     _call("thn_attention_prefill_bf16", _ptr(out), _ptr(q), _ptr(tiles.row0), _ptr(tiles.rows),
           tiles.n, _ptr(rows.row_slot), _ptr(rows.row_pos), _ptr(kv.storage), _ptr(kv.block_table),
           kv.block_table.shape[1], kv.n_kv, kv.page_size, kv.head_dim, n_q, float(scale), int(window or 0),
-          int(keep_first or 0), int(chunk or 0), int(bool(split_weights)), _ptr(err), _stream())
+          int(keep_first or 0), int(chunk or 0), int(bool(split_weights)), *shape.args(), _ptr(err), _stream())
     return out
 
 
@@ -865,7 +940,8 @@ def decode_hints(rows: StepRows, n_kv: int, n_splits: int, device) -> int:
 def attention_decode_bf16(q: torch.Tensor, rows: StepRows, kv: KVView, n_q: int, scale: float,
                           window: Optional[int], err: torch.Tensor, n_splits: Optional[int] = None,
                           scratch: Optional[torch.Tensor] = None, fused_merge: bool = True,
-                          keep_first: int = 0, chunk: Optional[int] = None, split_weights: bool = False) -> torch.Tensor:
+                          keep_first: int = 0, chunk: Optional[int] = None, split_weights: bool = False,
+                          shape: ScoreShape = PLAIN_SCORES) -> torch.Tensor:
     """Split-KV flash decoding: one token per sequence.  Partial results of the splits go
     through float32 scratch memory, which is allocated here unless given."""
     _need(q, "attention q", torch.bfloat16)
@@ -883,7 +959,7 @@ def attention_decode_bf16(q: torch.Tensor, rows: StepRows, kv: KVView, n_q: int,
     _call("thn_attention_decode_bf16", _ptr(out), _ptr(q), _ptr(rows.row_slot), _ptr(rows.row_pos),
           _ptr(kv.storage), _ptr(kv.block_table), kv.block_table.shape[1], kv.n_kv, kv.page_size, kv.head_dim,
           n_seqs, n_q, n_splits, float(scale), int(window or 0), int(keep_first or 0), int(chunk or 0),
-          int(bool(split_weights)), _ptr(scratch), _ptr(counters),
+          int(bool(split_weights)), *shape.args(), _ptr(scratch), _ptr(counters),
           kv.storage.shape[0], decode_hints(rows, kv.n_kv, n_splits, q.device), _ptr(err), _stream())
     return out
 
@@ -1128,10 +1204,15 @@ class Routing:
     chosen_weight: torch.Tensor   # float32 [rows, top]
 
 
-def moe_route(logits: torch.Tensor, n_experts: int, n_groups: int, keep: int, top: int, scale: float) -> Routing:
+SCORINGS = {"softmax": 0, "logistic": 1}
+
+
+def moe_route(logits: torch.Tensor, n_experts: int, n_groups: int, keep: int, top: int, scale: float,
+              scoring: str = "softmax") -> Routing:
     """Routing weights from float32 router logits (the first ``n_experts`` columns of
-    ``logits``): softmax over all experts, the ``keep`` best of ``n_groups`` groups of neighbours
-    (a group's score is its largest), the ``top`` best allowed experts, weights ``score * scale``."""
+    ``logits``): scores by softmax over all experts or (``scoring`` "logistic") the logistic
+    function of each logit, the ``keep`` best of ``n_groups`` groups of neighbours (a group's
+    score is its largest), the ``top`` best allowed experts, weights ``score * scale``."""
     _need(logits, "moe_route logits", torch.float32)
     rows = logits.shape[0]
     if logits.shape[1] < n_experts:
@@ -1140,8 +1221,32 @@ def moe_route(logits: torch.Tensor, n_experts: int, n_groups: int, keep: int, to
     chosen = torch.empty((rows, top), dtype=torch.int32, device=logits.device)
     weight = torch.empty((rows, top), dtype=torch.float32, device=logits.device)
     _call("thn_moe_route", _ptr(dense), _ptr(chosen), _ptr(weight), _ptr(logits), logits.shape[1], rows, n_experts,
-          n_groups, keep, top, float(scale), _stream())
+          n_groups, keep, top, float(scale), SCORINGS[scoring], _stream())
     return Routing(dense, chosen, weight)
+
+
+def routed_clamped_glu(gu: torch.Tensor, routing: Routing, ff: int, shared_ff: int, limit: float, shared_limit: float,
+                       alpha: float, shared_logit: Optional[torch.Tensor] = None, logit_column: int = 0) -> torch.Tensor:
+    """Experts ``g * logistic(alpha * g) * (u + 1)`` with ``g = min(w * gate, limit)`` and
+    ``u = clamp(w * up, -limit, limit)``, ``w`` the routing weight of the column's expert: the
+    expert sees the token times its weight, and its projections are linear.  ``gu`` [rows,
+    2 * (experts * ff + shared_ff)] holds the gates of all columns, then the ups.  The shared
+    expert's columns take ``w = 1`` and ``shared_limit`` and are multiplied by
+    ``logistic(shared_logit[:, logit_column])`` (no gate without ``shared_logit``); columns of an
+    expert that was not chosen are zero.  Returns [rows, experts * ff + shared_ff]."""
+    _need(gu, "routed_clamped_glu gu")
+    rows, n_experts = routing.dense.shape
+    width = n_experts * ff + shared_ff
+    if tuple(gu.shape) != (rows, 2 * width):
+        raise KernelError(f"routed_clamped_glu: gu is {tuple(gu.shape)}, expected {(rows, 2 * width)}")
+    logit_ptr, stride = None, 0
+    if shared_logit is not None:
+        _need(shared_logit, "routed_clamped_glu gate logits", torch.float32)
+        logit_ptr, stride = shared_logit.data_ptr() + 4 * logit_column, shared_logit.shape[1]
+    out = torch.empty((rows, width), dtype=gu.dtype, device=gu.device)
+    _call("thn_routed_clamped_glu", _ptr(out), _ptr(gu), _ptr(routing.dense), logit_ptr, stride, rows, n_experts, ff,
+          shared_ff, float(limit), float(shared_limit or 1.0), float(alpha), _code(gu, "routed_clamped_glu"), _stream())
+    return out
 
 
 def routed_gelu(u: torch.Tensor, routing: Routing, ff: int, shared_ff: int,
@@ -1206,5 +1311,5 @@ def gather_i32(src: torch.Tensor, index: torch.Tensor, out: Optional[torch.Tenso
 __all__ = [
     "KernelError", "KernelLibraryError", "KVView", "RotaryTables", "RowTiles", "StepRows", "row_tiles_of", "prompt_attention_tile", "linear_stream", "linear_swiglu", "linear_tcgen05", "add_rmsnorm", "advance",
     "ROW_TILE", "attention", "attention_decode_bf16", "attention_generic", "attention_prefill_bf16", "attention_prefill_tcgen05", "decode_splits", "choose_tokens", "gather_i32", "gather_rows", "lib", "linear", "new_error_word",
-    "qk_norm_rope_cache", "qk_prepare", "Gain", "STREAM_AS_IS", "residual_norm", "gather_rows_scaled", "logistic_gate", "latent_norm", "latent_assemble", "mlstm", "mlstm_column_blocks", "set_mlstm_kernel", "Routing", "moe_route", "routed_gelu", "gated_head_norm", "clamped_glu", "DeltaShape", "delta_rule", "qkv_attention", "raise_on_device_error", "rmsnorm", "rope_table", "scatter_i32", "step_rows", "swiglu",
+    "qk_norm_rope_cache", "qk_prepare", "Gain", "STREAM_AS_IS", "residual_norm", "gather_rows_scaled", "logistic_gate", "latent_norm", "latent_assemble", "mlstm", "mlstm_column_blocks", "set_mlstm_kernel", "Routing", "moe_route", "routed_gelu", "gated_head_norm", "clamped_glu", "routed_clamped_glu", "polynorm", "scale_", "ScoreShape", "PLAIN_SCORES", "DeltaShape", "delta_rule", "qkv_attention", "raise_on_device_error", "rmsnorm", "rope_table", "scatter_i32", "step_rows", "swiglu",
 ]

@@ -26,6 +26,14 @@ query's and key's.  ``chunk`` (instead of ``window``): position i sees j <= i on
 ``floor(i / chunk) = floor(j / chunk)``, chunks counted from the sequence's first position.
 ``softmax_weights`` "float32": the weights stay float32 where they multiply the values, in
 the kernels that do not put that product on tensor cores.
+
+``softcap`` (a positive number): a score s becomes ``softcap * tanh(s / softcap)`` before the
+softmax.  ``q_temp`` (a mapping ``coef, every``): the query at position p is multiplied by
+``1 + coef * ln(floor((p + 1) / every) + 1)``; the kernels apply the factor to the row's scores in
+float32.  ``kv`` "own" (default) or "shared": a "shared" mixer has no key and value projections
+at all (no ``k_proj`` and ``v_proj`` tensors); every schedule entry that runs it reads the cache
+that another layer wrote (``writes_cache=False``), with its own queries, scale, mask and score
+shaping.
 """
 
 from __future__ import annotations
@@ -49,10 +57,11 @@ class Attention:
         p = spec.params
         hidden, n_q, n_kv, d = int(p["hidden_size"]), int(p["n_heads"]), int(p["n_kv_heads"]), int(p["head_dim"])
         dv = int(p.get("value_dim") or d)
-        specs = [TensorSpec(spec.tensors["q_proj"], (n_q * d, hidden), MATRIX),
-                 TensorSpec(spec.tensors["k_proj"], (n_kv * d, hidden), MATRIX)]
-        if p.get("values", "projection") == "projection":
-            specs.append(TensorSpec(spec.tensors["v_proj"], (n_kv * dv, hidden), MATRIX))
+        specs = [TensorSpec(spec.tensors["q_proj"], (n_q * d, hidden), MATRIX)]
+        if p.get("kv", "own") != "shared":
+            specs.append(TensorSpec(spec.tensors["k_proj"], (n_kv * d, hidden), MATRIX))
+            if p.get("values", "projection") == "projection":
+                specs.append(TensorSpec(spec.tensors["v_proj"], (n_kv * dv, hidden), MATRIX))
         specs.append(TensorSpec(spec.tensors["o_proj"], (hidden, n_q * dv), MATRIX))
         if p.get("qk_norm_eps") is not None:
             whole = p.get("qk_norm_scope", "head") == "projection"
@@ -80,10 +89,22 @@ class Attention:
             raise ValueError(f"attention: qk_norm_scope {p.get('qk_norm_scope')!r} or values {p.get('values')!r} unknown")
         if self.values_are_keys and self.value_dim != self.head_dim:
             raise ValueError("attention: values that are the keys have the keys' size")
-        projections = [runtime.tensor(spec, "q_proj"), runtime.tensor(spec, "k_proj")]
-        if not self.values_are_keys:
-            projections.append(runtime.tensor(spec, "v_proj"))
-        self.w_qkv = torch.cat(projections, dim=0).contiguous()
+        if p.get("kv", "own") not in ("own", "shared"):
+            raise ValueError(f"attention: kv {p.get('kv')!r} is neither 'own' nor 'shared'")
+        self.shared_kv = p.get("kv", "own") == "shared"
+        if self.shared_kv and (p.get("qk_norm_eps") is not None or p.get("position") is not None):
+            raise ValueError("attention: a mixer without keys of its own has no q/k norm and no rotation here")
+        projections = [runtime.tensor(spec, "q_proj")]
+        if not self.shared_kv:
+            projections.append(runtime.tensor(spec, "k_proj"))
+            if not self.values_are_keys:
+                projections.append(runtime.tensor(spec, "v_proj"))
+        self.w_qkv = torch.cat(projections, dim=0).contiguous() if len(projections) > 1 else projections[0]
+        temp = p.get("q_temp")
+        self.shape = ops.ScoreShape(float(p.get("softcap") or 0.0), float(temp["coef"]) if temp else 0.0,
+                                    int(temp["every"]) if temp else 0)
+        if self.shape.softcap < 0 or self.shape.temp_every < 0:
+            raise ValueError("attention: softcap and q_temp.every are positive")
         self.w_o = runtime.tensor(spec, "o_proj")
         self.q_gain = runtime.tensor(spec, "q_norm") if self.eps is not None else None
         self.k_gain = runtime.tensor(spec, "k_norm") if self.eps is not None else None
@@ -104,6 +125,8 @@ class Attention:
             self.q_gain, self.k_gain = self.q_gain.float().contiguous(), self.k_gain.float().contiguous()
 
     def cache_need(self) -> CacheNeed:
+        if self.shared_kv:
+            return None
         return KVSpec(self.n_kv, self.head_dim, self.window, self.keep_first, self.chunk, self.value_dim)
 
     def _tile(self, page_size: int) -> int:
@@ -128,7 +151,14 @@ class Attention:
             if row0 is not None:
                 tiles = ops.RowTiles(row0, ctx.inputs[f"row_tiles/{size}/rows"], row0.shape[0], size)
         qkv = ops.linear(x, self.w_qkv, err=ctx.err)
-        if self.general or self.keep_first or self.chunk or self.exact_weights:
+        if self.shared_kv:
+            if entry.writes_cache:
+                raise ValueError("attention: a mixer without keys of its own cannot write a cache")
+            # the projected rows are the queries: nothing to normalise, rotate or store
+            a = ops.attention(qkv, ctx.rows, kv, self.n_q, self.scale, self.window, ctx.err, tiles, self.keep_first,
+                              self.chunk, self.exact_weights, self.shape)
+            return ops.linear(a, self.w_o, err=ctx.err)
+        if self.general or self.keep_first or self.chunk or self.exact_weights or self.shape.active:
             rotary = self.position.tables() if self.position is not None else None
             if self.general:
                 q = ops.qk_prepare(qkv, self.q_gain, self.k_gain, self.norm_scope, self.eps or 1.0, rotary, ctx.rows, kv,
@@ -137,7 +167,7 @@ class Attention:
                 q = ops.qk_norm_rope_cache(qkv, self.q_gain, self.k_gain, self.eps if self.eps is not None else 1.0,
                                            rotary, ctx.rows, kv, self.n_q, entry.writes_cache, ctx.err)
             a = ops.attention(q, ctx.rows, kv, self.n_q, self.scale, self.window, ctx.err, tiles, self.keep_first,
-                              self.chunk, self.exact_weights)
+                              self.chunk, self.exact_weights, self.shape)
             return ops.linear(a, self.w_o, err=ctx.err)
         a = ops.qkv_attention(qkv, self.q_gain, self.k_gain, self.eps if self.eps is not None else 1.0,
                               self.position.tables() if self.position is not None else None,

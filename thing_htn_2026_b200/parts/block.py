@@ -17,6 +17,12 @@ still has to pass, so that this norm, the add and the next norm are one kernel.
 itself: ``a = x + norm(mixer(x))``, ``y = a + norm'(ffn(a))``, over a float32 stream; the
 feed-forward half may be absent.  The pending output again travels as a :class:`Branch`, and
 "norm of the branch, add, round the sum for the next sublayer" is one kernel.
+
+``parallel``: one norm per layer, read by both sublayers: ``n = norm(x)``,
+``y = x + factor * (mixer(n) + ffn(n))`` over a float32 stream (``factor`` a parameter of the
+block, default 1; the feed-forward may be absent).  The two outputs travel as one
+:class:`Branch` with its second tensor and its factor, so that "add both, times the factor, into
+the stream, norm of the sum" is one kernel at the next layer's norm or at the model's last.
 """
 
 from __future__ import annotations
@@ -124,3 +130,25 @@ class BranchNormBlock(Block):
             return h, a
         x = self.norm_mixer.add_read(h, a.tensor)
         return h, Branch(self.ffn.forward(x, ctx), self.norm_ffn)
+
+
+@register_part("block", "parallel")
+class ParallelBlock(Block):
+    MEMBERS = {"norm": "norm", "mixer": "mixer", "ffn": "ffn"}
+
+    def __init__(self, spec: PartSpec, runtime: Runtime):
+        super().__init__(spec, runtime)
+        self.factor = float(spec.params.get("factor", 1.0))
+
+    def forward(self, h: torch.Tensor, d, ctx: StepContext, entry: ScheduleEntry):
+        if h.dtype != torch.float32:
+            raise TypeError("parallel: the residual stream must start in float32 (an embedding with stream 'float32')")
+        if d is None:
+            n = self.norm.forward(h)
+        elif isinstance(d, Branch):
+            n = self.norm.add_forward(h, d, post=d.norm)
+        else:
+            n = self.norm.add_forward(h, d)
+        a = self.mixer.forward(n, ctx, entry)
+        f = self.ffn.forward(n, ctx) if self.ffn is not None else None
+        return h, Branch(a, None, f, self.factor)

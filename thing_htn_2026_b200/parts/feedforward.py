@@ -15,7 +15,21 @@ the same form runs for every token and is added, multiplied by ``logistic(shared
 number per token; ``shared_gated`` False: added as it is).  The up-projections of all experts are
 one product, the activation carries the routing weights (zero for an expert that was not chosen),
 and one down-projection over all experts' columns sums the chosen ones: the result does not
-depend on the other rows of the step.  Kernels: csrc/moe.cu."""
+depend on the other rows of the step.  Kernels: csrc/moe.cu.
+
+``polynorm``: ``down(act(up(x)))`` with ``act(z) = a N(z) + b N(z^2) + c N(z^3) + e``, powers
+taken entry by entry and ``N`` the division of a token's vector by its root mean square (``eps``
+inside the root); the four numbers are a tensor of the layer (``act``).
+
+``routed_clamped_experts``: a mixture whose experts have the form of ``clamped_glu`` (``limit``,
+``slope``).  Scores are ``logistic(router(x))``, each expert by itself, in float32; the ``top``
+largest are chosen and weighted by their scores as they are.  The weight multiplies the expert's
+*input*: the output is the sum of ``expert(w x)``.  Because the projections are linear, the gate
+and up projections of all experts are one product over ``x`` and the activation kernel multiplies
+the projected values by ``w`` before the clamps; one down-projection over all experts' columns
+sums the chosen ones.  With ``shared_ff`` a shared expert with a limit of its own
+(``shared_limit``) runs for every token on the token itself and is added times
+``logistic(shared_gate(x))``."""
 
 from __future__ import annotations
 
@@ -25,7 +39,7 @@ import torch
 
 from .. import ops
 from ..config.base import PartSpec
-from ..weights.loader import MATRIX, TensorSpec
+from ..weights.loader import GAIN, MATRIX, TensorSpec
 from .registry import register_part
 from .runtime import Runtime
 
@@ -115,3 +129,79 @@ class RoutedExperts:
         u = ops.linear(x, self.w_up, err=err)
         a = ops.routed_gelu(u, routing, self.ff, self.shared_ff, z if self.shared_gated else None, self.n_experts)
         return ops.linear(a, self.w_down, err=err)
+
+
+@register_part("ffn", "polynorm")
+class PolyNormFFN:
+    @classmethod
+    def tensor_specs(cls, spec: PartSpec) -> List[TensorSpec]:
+        hidden, inter = int(spec.params["hidden_size"]), int(spec.params["intermediate_size"])
+        return [TensorSpec(spec.tensors["up_proj"], (inter, hidden), MATRIX),
+                TensorSpec(spec.tensors["down_proj"], (hidden, inter), MATRIX),
+                TensorSpec(spec.tensors["act"], (4,), GAIN, init="polynomial")]
+
+    def __init__(self, spec: PartSpec, runtime: Runtime):
+        self.eps = float(spec.params["eps"])
+        self.w_up = runtime.tensor(spec, "up_proj")
+        self.w_down = runtime.tensor(spec, "down_proj")
+        self.coefficients = runtime.tensor(spec, "act").to(torch.float32).contiguous()
+
+    def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
+        err = getattr(ctx, "err", None)
+        return ops.linear(ops.polynorm(ops.linear(x, self.w_up, err=err), self.coefficients, self.eps), self.w_down, err=err)
+
+
+@register_part("ffn", "routed_clamped_experts")
+class RoutedClampedExperts:
+    @staticmethod
+    def _sizes(spec: PartSpec):
+        p = spec.params
+        return int(p["hidden_size"]), int(p["n_experts"]), int(p["expert_ff"]), int(p.get("shared_ff") or 0)
+
+    @classmethod
+    def tensor_specs(cls, spec: PartSpec) -> List[TensorSpec]:
+        hidden, n, ff, shared = cls._sizes(spec)
+        specs = [TensorSpec(spec.tensors["router"], (n, hidden), MATRIX)]
+        for e in range(n):
+            specs += [TensorSpec(spec.tensors[f"gate.{e}"], (ff, hidden), MATRIX),
+                      TensorSpec(spec.tensors[f"up.{e}"], (ff, hidden), MATRIX),
+                      TensorSpec(spec.tensors[f"down.{e}"], (hidden, ff), MATRIX)]
+        if shared:
+            specs += [TensorSpec(spec.tensors["shared_gate_proj"], (shared, hidden), MATRIX),
+                      TensorSpec(spec.tensors["shared_up"], (shared, hidden), MATRIX),
+                      TensorSpec(spec.tensors["shared_down"], (hidden, shared), MATRIX)]
+            if spec.params.get("shared_gated", True):
+                specs.append(TensorSpec(spec.tensors["shared_gate"], (1, hidden), MATRIX))
+        return specs
+
+    def __init__(self, spec: PartSpec, runtime: Runtime):
+        p = spec.params
+        _, self.n_experts, self.ff, self.shared_ff = self._sizes(spec)
+        self.top = int(p["top"])
+        if not 0 < self.top <= self.n_experts:
+            raise ValueError(f"routed_clamped_experts: top {self.top} of {self.n_experts} experts")
+        self.limit, self.slope = float(p["limit"]), float(p["slope"])
+        self.shared_limit = float(p.get("shared_limit") or self.limit)
+        self.shared_gated = bool(self.shared_ff) and bool(p.get("shared_gated", True))
+        gates = [runtime.tensor(spec, f"gate.{e}") for e in range(self.n_experts)]
+        ups = [runtime.tensor(spec, f"up.{e}") for e in range(self.n_experts)]
+        downs = [runtime.tensor(spec, f"down.{e}") for e in range(self.n_experts)]
+        route = [runtime.tensor(spec, "router")]
+        if self.shared_ff:
+            gates.append(runtime.tensor(spec, "shared_gate_proj"))
+            ups.append(runtime.tensor(spec, "shared_up"))
+            downs.append(runtime.tensor(spec, "shared_down"))
+        if self.shared_gated:
+            route.append(runtime.tensor(spec, "shared_gate"))
+        self.w_gate_up = torch.cat(gates + ups, dim=0).contiguous()     # the gates of all columns, then the ups
+        self.w_down = torch.cat(downs, dim=1).contiguous()
+        self.w_route = torch.cat(route, dim=0).contiguous()
+
+    def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
+        err = getattr(ctx, "err", None)
+        z = ops.linear(x, self.w_route, out_dtype=torch.float32, err=err)
+        routing = ops.moe_route(z, self.n_experts, 1, 1, self.top, 1.0, scoring="logistic")
+        gu = ops.linear(x, self.w_gate_up, err=err)
+        y = ops.routed_clamped_glu(gu, routing, self.ff, self.shared_ff, self.limit, self.shared_limit, self.slope,
+                                   z if self.shared_gated else None, self.n_experts)
+        return ops.linear(y, self.w_down, err=err)

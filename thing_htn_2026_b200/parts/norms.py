@@ -7,7 +7,11 @@ which multiplies as ``1 + w``); ``residual`` (default: the activation type; "flo
 stream this norm reads is kept in float32 whatever the activation type, and every sum of the
 norm is float32 with one rounding at the output).  With a float32 stream, ``add_forward``
 also takes ``post``: another norm of this kind that the branch's output passes before it is
-added (norms on both sides of a sublayer), in the same kernel.
+added (norms on both sides of a sublayer), in the same kernel.  ``groups`` (default 1; float32
+stream only): the row is split into that many equal consecutive parts, each divided by its own
+``sqrt(mean(part^2) + eps)``, and the whole is multiplied by the gain.  ``add_forward`` takes a
+:class:`Branch` as well: its second tensor and its factor are added in the same kernel,
+``h <- h + factor * (d + d')``.
 
 ``layernorm``: ``(x - mean) / sqrt(var + eps) * w + b`` with the variance as the mean of the
 squared deviations, over a float32 stream only.  Besides the calls above it has ``read`` and
@@ -25,7 +29,7 @@ from .. import ops
 from ..config.base import PartSpec
 from ..weights.loader import GAIN, TensorSpec
 from .registry import register_part
-from .runtime import Runtime
+from .runtime import Branch, Runtime
 
 
 @register_part("norm", "rmsnorm")
@@ -40,10 +44,13 @@ class RMSNorm:
         self.eps = float(spec.params["eps"])
         self.offset = float(spec.params.get("gain_offset", 0.0))
         self.float32_stream = spec.params.get("residual") == "float32"
+        self.groups = int(spec.params.get("groups") or 1)
+        if self.groups < 1 or self.size % self.groups or (self.groups > 1 and not self.float32_stream):
+            raise ValueError(f"rmsnorm: {self.groups} groups must divide the size {self.size} and need a float32 stream")
         self.dtype = runtime.dtype
         self.gain = runtime.tensor(spec, "weight")
         if self.float32_stream or self.offset:
-            self.as_gain = ops.Gain(self.gain.to(torch.float32).contiguous(), self.offset, self.eps)
+            self.as_gain = ops.Gain(self.gain.to(torch.float32).contiguous(), self.offset, self.eps, groups=self.groups)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         if self.float32_stream or self.offset:
@@ -57,7 +64,12 @@ class RMSNorm:
         """``x`` of the activation type starts a float32 stream: returns (stream, norm of it)."""
         return ops.residual_norm(None, x, None, self.as_gain, self.dtype)
 
-    def add_forward(self, h: torch.Tensor, d: torch.Tensor, post: Optional["RMSNorm"] = None) -> torch.Tensor:
+    def add_forward(self, h: torch.Tensor, d, post: Optional["RMSNorm"] = None) -> torch.Tensor:
+        if isinstance(d, Branch):       # a branch with a second tensor or a factor (its norm comes as ``post``)
+            if not self.float32_stream:
+                raise ops.KernelError("rmsnorm: a branch of two tensors or with a factor needs a float32 stream")
+            return ops.residual_norm(h, d.tensor, post.as_gain if post is not None else None, self.as_gain, self.dtype,
+                                     d2=d.second, mult=d.factor)[1]
         if self.float32_stream:
             return ops.residual_norm(h, d, post.as_gain if post is not None else None, self.as_gain, self.dtype)[1]
         if post is not None or self.offset:

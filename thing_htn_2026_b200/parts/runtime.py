@@ -29,10 +29,14 @@ class Runtime:
 class Branch:
     """A sublayer's output that has not been added to the residual stream yet, with the norm
     it passes before the add (None: it is added as it is).  Blocks hand it on in place of a bare
-    tensor when the add is to be fused into the next norm."""
+    tensor when the add is to be fused into the next norm.  ``second``: the output of a sublayer
+    that ran beside the first on the same input, added with it; ``factor``: what multiplies
+    the branch as it is added."""
 
     tensor: torch.Tensor
     norm: Optional[object] = None
+    second: Optional[torch.Tensor] = None
+    factor: float = 1.0
 
 
 @dataclass(frozen=True)

@@ -69,11 +69,16 @@ def _gate_bias(t, generator, matrix_std, gain_std):
     return t.uniform_(0.0, 1.0, generator=generator).mul_(7.0).sub_(2.0)
 
 
+def _polynomial(t, generator, matrix_std, gain_std):
+    """Coefficients of a polynomial activation and its constant: of the order of one half, either sign."""
+    return t.uniform_(-1.0, 1.0, generator=generator).mul_(0.7)
+
+
 # How a tensor is drawn, by the name in ``TensorSpec.init``.  ``fill(t, generator, matrix_std,
 # gain_std)`` fills ``t`` (float32 on the CPU, the held dtype on a device) in place.
 INITIALIZERS: Dict[str, Callable] = {"normal": _normal, "one_plus_normal": _one_plus_normal, "zeros": _zeros,
                                      "zero_centered": _zero_centered, "conv_taps": _conv_taps, "log_rate": _log_rate,
-                                     "unit_normal": _unit_normal, "small_normal": _small_normal, "gate_bias": _gate_bias}
+                                     "unit_normal": _unit_normal, "small_normal": _small_normal, "gate_bias": _gate_bias, "polynomial": _polynomial}
 # The rule of a spec that names none, by its role.
 ROLE_INIT = {MATRIX: "normal", GAIN: "one_plus_normal", TABLE: "zeros"}
 
