@@ -250,3 +250,14 @@ def greedy(config, tensors, prompt, n_new, precision=torch.float64):
     for _ in range(n_new):
         out.append(int(forward(config, tensors, out, precision)[-1].argmax()))
     return out[len(prompt):]
+
+
+_models = {}
+
+
+def model_logits(folder, tokens, precision=torch.float32):
+    """Logits [T, vocab] (float32) of one whole sequence through the model stored in ``folder``."""
+    if folder not in _models:
+        _models[folder] = read_model(folder)
+    config, tensors = _models[folder]
+    return forward(config, tensors, list(tokens), precision).to(torch.float32)

@@ -58,6 +58,36 @@ __global__ void __launch_bounds__(kRouteWarps * 32) moe_route_kernel(
     const float* zr = z + (size_t)row * z_stride;
     const int per = n_experts / n_groups;
 
+    if (scoring == 1 && keep >= n_groups) {
+        // Logistic scores of experts that are all eligible: the order of the scores is the order
+        // of the logits, and the logits do not saturate, so the choice is made on them.
+        for (int e = lane; e < n_experts; e += 32) {
+            s[e] = zr[e];
+            dense[(size_t)row * n_experts + e] = 0.f;
+        }
+        __syncwarp();
+        for (int pick = 0; pick < top; ++pick) {
+            Best b{-INFINITY, 0x7fffffff};
+            for (int e = lane; e < n_experts; e += 32)
+                if (s[e] > b.value || (s[e] == b.value && e < b.index)) { b.value = s[e]; b.index = e; }
+            b = warp_best(b);
+            __syncwarp();
+            if (lane == 0) {
+                if (b.index < n_experts) {
+                    const float w = scale / (1.0f + expf(-b.value));
+                    dense[(size_t)row * n_experts + b.index] = w;
+                    chosen[(size_t)row * top + pick] = b.index;
+                    chosen_weight[(size_t)row * top + pick] = w;
+                    s[b.index] = -INFINITY;       // taken
+                } else {                      // no logit compares (not a number): an index that exists, no weight
+                    chosen[(size_t)row * top + pick] = pick;
+                    chosen_weight[(size_t)row * top + pick] = 0.f;
+                }
+            }
+            __syncwarp();
+        }
+        return;
+    }
     if (scoring == 1) {
         for (int e = lane; e < n_experts; e += 32) {
             s[e] = 1.0f / (1.0f + expf(-zr[e]));
