@@ -28,7 +28,11 @@ and every kernel of the new design alone (cold caches) beside the like kernel of
 path, each with the fraction of its roofline.  ``--design bunudra`` does the same for the Bunudra
 decoder (``bunudra-w2048``, ``bunudra-w4096``: matrix-memory, chunked-attention and
 latent-attention layers with routed experts) beside a Lanilix decoder of the same width, depth,
-heads and feed-forward weights, its closest relative here.  The default run is untouched by both.
+heads and feed-forward weights, its closest relative here.  ``--design ditilix`` measures the
+Ditilix decoder (``ditilix-w2048``, ``ditilix-w4096``: attention over all keys with a score cap and a
+query temperature, every other layer reading the keys of the layer before it, one dense
+feed-forward with a polynomial of norms and seven routed ones) beside a Qwen3 decoder of the same
+width, depth, heads and feed-forward products.  The default run is untouched by all three.
 """
 
 from __future__ import annotations
@@ -889,6 +893,162 @@ def bunudra_kernel_table(torch, bun, peak, batch, context):
     return rows
 
 
+DITILIX_SIZES = ("ditilix-w2048", "ditilix-w4096")
+
+
+def qwen3_like_ditilix(dit):
+    """A Qwen3 config.json of the same width, depth, vocabulary, heads and head size as a Ditilix
+    configuration, with a gated feed-forward as wide as all experts of a routed layer together
+    (the routed layers run every expert's columns as one product, so the products are equal)."""
+    m = dit["layers"][0]["mixer"]
+    mlp = next(l["mlp"] for l in dit["layers"] if l["mlp"] and l["mlp"]["kind"] == "moe")
+    ff = mlp["router"]["experts"] * mlp["expert"]["ff"] + (mlp.get("shared") or {}).get("ff", 0)
+    return {"architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "hidden_act": "silu", "attention_bias": False,
+            "rope_scaling": None, "vocab_size": dit["vocab"], "hidden_size": dit["width"], "intermediate_size": ff,
+            "num_hidden_layers": len(dit["layers"]), "num_attention_heads": m["heads"],
+            "num_key_value_heads": m["kv_heads"], "head_dim": m["dim"], "rms_norm_eps": dit["norm"]["eps"],
+            "rope_theta": 1000000.0, "tie_word_embeddings": False, "max_position_embeddings": 8192}
+
+
+def ditilix_kernel_table(torch, dit, peak, batch, context):
+    """Every kernel of the Ditilix design alone, beside the like kernel of the Qwen3 path (of the
+    Bunudra path for the router), cold caches (a buffer larger than L2 is written between timed
+    launches): microseconds, and the fraction of the roofline that the kernel's algorithmic bytes
+    or flops amount to."""
+    from thing_htn_2026_b200 import ops
+    from thing_htn_2026_b200.cache import KVSpec, SequenceCache
+    dev, bf = "cuda:0", torch.bfloat16
+    attn = dit["layers"][0]["mixer"]
+    dense = next(l["mlp"] for l in dit["layers"] if l["mlp"] and l["mlp"]["kind"] == "dense")
+    mlp = next(l["mlp"] for l in dit["layers"] if l["mlp"] and l["mlp"]["kind"] == "moe")
+    W, T, V = dit["width"], PREFILL_TOKENS, dit["vocab"]
+    groups, mult = dit["norm"]["groups"], dit["residual_mult"]
+    E, ff, top = mlp["router"]["experts"], mlp["expert"]["ff"], mlp["router"]["top"]
+    sff = (mlp.get("shared") or {}).get("ff", 0)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    hbm, tensor = peak["hbm_gbs"] * 1e9, peak["bf16_tflops"] * 1e12
+
+    def timed(fn, reps=7):
+        out = []
+        for _ in range(reps):
+            flush.zero_()
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            fn()
+            end.record()
+            torch.cuda.synchronize()
+            out.append(start.elapsed_time(end) * 1e3)
+        return statistics.median(out[2:])
+
+    rows = {}
+
+    def row(name, fn, nbytes=0, flops=0, like=None):
+        us = timed(fn)
+        t_roof = max(nbytes / hbm, flops / tensor) * 1e6
+        rows[name] = {"us": round(us, 2), "roofline_us": round(t_roof, 2), "frac": round(t_roof / us, 3), "like": like,
+                      "bound": "hbm" if nbytes / hbm >= flops / tensor else "flops"}
+
+    g = torch.Generator(device=dev).manual_seed(0)
+    rnd = lambda *shape: torch.randn(shape, generator=g, device=dev)
+    err = ops.new_error_word(dev)
+    table = rnd(V, W).to(bf)
+    pair = torch.arange((W + 1) // 2, dtype=torch.float64, device=dev)
+    frequencies = 10000.0 ** (-2.0 * pair / W)
+    for n, tag in ((T, "prefill"), (batch, "decode")):
+        # ---- the rows that start the stream: float32 rows with sinusoidal positions, against bfloat16 rows as they are
+        index = torch.randint(0, V, (n,), generator=g, device=dev).to(torch.int32)
+        positions = torch.arange(n, dtype=torch.int32, device=dev) + context
+        row(f"{tag}: gather_rows_scaled (float32 rows, sinusoidal positions)",
+            lambda: ops.gather_rows_scaled(table, index, 1.0, err, positions, frequencies), nbytes=n * W * (2 + 4),
+            like=f"{tag}: gather_rows")
+        row(f"{tag}: gather_rows", lambda: ops.gather_rows(table, index, err), nbytes=n * W * 4)
+        # ---- the one norm of a layer: both branches times a factor into the float32 stream, a norm in groups
+        h32, a16, b16 = rnd(n, W), rnd(n, W).to(bf), rnd(n, W).to(bf)
+        grouped = ops.Gain(1 + rnd(W) * 0.1, 0.0, 1e-6, groups=groups)
+        h16, w16 = rnd(n, W).to(bf), (1 + rnd(W) * 0.1).to(bf)
+        row(f"{tag}: residual_norm (two branches, a factor, {groups} groups)",
+            lambda: ops.residual_norm(h32, a16, None, grouped, bf, d2=b16, mult=mult), nbytes=n * W * (4 + 4 + 2 + 2 + 2),
+            like=f"{tag}: add_rmsnorm")
+        row(f"{tag}: add_rmsnorm", lambda: ops.add_rmsnorm(h16, a16, w16, 1e-6), nbytes=n * W * (2 + 2 + 2 + 2))
+        # ---- activations: the polynomial of norms and the routed clamped unit, against the gated unit
+        z = rnd(n, dense["ff"]).to(bf)
+        coefficients = torch.tensor([0.5, 0.3, 0.2, 0.1], device=dev)
+        gu = rnd(n, 2 * (E * ff + sff)).to(bf)
+        logits = rnd(n, E + 1)
+        routing = ops.moe_route(logits, E, 1, 1, top, 1.0, scoring="logistic")
+        row(f"{tag}: polynorm", lambda: ops.polynorm(z, coefficients, 1e-6), nbytes=n * dense["ff"] * 4, like=f"{tag}: swiglu")
+        row(f"{tag}: routed_clamped_glu",
+            lambda: ops.routed_clamped_glu(gu, routing, ff, sff, mlp["expert"]["limit"], mlp["expert"]["limit"], 1.702,
+                                           logits, E),
+            nbytes=n * (2 * (top * ff + sff) * 2 + (E * ff + sff) * 2), like=f"{tag}: swiglu")
+        row(f"{tag}: swiglu", lambda: ops.swiglu(gu), nbytes=n * (E * ff + sff) * 6)
+        row(f"{tag}: moe_route (logistic scores)", lambda: ops.moe_route(logits, E, 1, 1, top, 1.0, scoring="logistic"),
+            nbytes=n * ((E + 1) * 4 + E * 4 + top * 8), like=f"{tag}: moe_route (softmax, groups)")
+        row(f"{tag}: moe_route (softmax, groups)", lambda: ops.moe_route(logits, E, 4 if E % 4 == 0 else 1, 2 if E % 4 == 0 else 1, top, 2.0),
+            nbytes=n * ((E + 1) * 4 + E * 4 + top * 8))
+
+    # ---- attention over a paged cache: one sequence of T tokens, then `batch` sequences at `context` keys
+    H, G, D = attn["heads"], attn["kv_heads"], attn["dim"]
+    shaped = ops.ScoreShape(float(attn.get("softcap") or 0.0), float(attn["q_temp"]["coef"]), int(attn["q_temp"]["every"]))
+    tables = ops.RotaryTables(torch.ones(8192, D // 2, device=dev), torch.zeros(8192, D // 2, device=dev), D, "half")
+    qg, kg = (1 + rnd(D) * 0.1).to(bf), (1 + rnd(D) * 0.1).to(bf)
+    width = (H + 2 * G) * D
+
+    def attention_rows(tags, prepare_of, shape, likes):
+        cache = SequenceCache([KVSpec(G, D, None, 0)], max_tokens=(batch * (context + 64) + T + 64), dtype=bf, device=dev,
+                              max_slots=batch + 2)
+        slots = cache.open(batch + 1)
+        prepare = prepare_of(cache)
+
+        def step_of(slot_list, counts):
+            cache.prepare(slot_list, counts)
+            cu = [0]
+            for c in counts:
+                cu.append(cu[-1] + c)
+            cu_dev = torch.tensor(cu, dtype=torch.int32, device=dev)
+            slots_dev = torch.tensor(slot_list, dtype=torch.int32, device=dev)
+            rows_ = ops.step_rows(cu_dev, slots_dev, cache.seq_lens, cu[-1], max(counts),
+                                  max_context=max(cache.length(s) + c for s, c in zip(slot_list, counts)),
+                                  lengths_differ=False)
+            return rows_, cu_dev, slots_dev
+
+        rows_, cu_dev, slots_dev = step_of([slots[0]], [T])
+        proj = rnd(T, width).to(bf)
+        size = ops.prompt_attention_tile(bf, D, cache.page_size, H, G)
+        r0, rn = ops.row_tiles_of([T], [0], size)
+        tiles = ops.RowTiles(torch.tensor(r0, dtype=torch.int32, device=dev), torch.tensor(rn, dtype=torch.int32, device=dev),
+                             len(r0), size)
+        row(f"prefill: {tags[0]}", lambda: prepare(proj, rows_), nbytes=T * width * 4, like=likes[0])
+        q = prepare(proj, rows_)
+        row(f"prefill: {tags[1]}", lambda: ops.attention(q, rows_, cache.kv_view(0), H, D ** -0.5, None, err, tiles, shape=shape),
+            flops=4.0 * H * D * T * (T + 1) / 2, nbytes=T * H * D * 4, like=likes[1])
+        others = slots[1:]
+        rows_, cu_dev, slots_dev = step_of(others, [context] * batch)
+        prepare(rnd(batch * context, width).to(bf), rows_)
+        ops.advance(cache.seq_lens, slots_dev, cu_dev)
+        cache.commit(others, [context] * batch)
+        rows_, cu_dev, slots_dev = step_of(others, [1] * batch)
+        proj1 = rnd(batch, width).to(bf)
+        row(f"decode: {tags[0]}", lambda: prepare(proj1, rows_), nbytes=batch * width * 4, like=likes[2])
+        q1 = prepare(proj1, rows_)
+        row(f"decode: {tags[1]}", lambda: ops.attention(q1, rows_, cache.kv_view(0), H, D ** -0.5, None, err, None, shape=shape),
+            nbytes=batch * G * (context + 1) * D * 2 * 2, like=likes[3])
+
+    qwen_tags = ("qk_norm_rope_cache", "attention (all keys)")
+    attention_rows(qwen_tags, lambda cache: (lambda proj, rows_: ops.qk_norm_rope_cache(proj, qg, kg, 1e-6, tables, rows_,
+                                                                                        cache.kv_view(0), H, True, err)),
+                   ops.PLAIN_SCORES, (None,) * 4)
+    attention_rows(("qk_prepare (no norm, no rotation)", "attention (all keys, score cap, query temperature)"),
+                   lambda cache: (lambda proj, rows_: ops.qk_prepare(proj, None, None, None, 1.0, None, rows_, cache.kv_view(0),
+                                                                     H, False, True, err)),
+                   shaped, tuple(f"{t}: {x}" for t in ("prefill", "decode") for x in qwen_tags))
+    ops.raise_on_device_error(err, "kernel table")
+    for name, r in rows.items():
+        if r["like"] in rows:
+            r["times_farther_than_like"] = round(rows[r["like"]]["frac"] / r["frac"], 2)
+    return rows
+
+
 def run_design(args):
     import torch
     from thing_htn_2026_b200 import Engine, ops
@@ -901,7 +1061,7 @@ def run_design(args):
     sampler.start()
     ops.launch_count = 0
     design = args.design
-    design_sizes = DESIGN_SIZES if design == "lanilix" else BUNUDRA_SIZES
+    design_sizes = {"lanilix": DESIGN_SIZES, "bunudra": BUNUDRA_SIZES, "ditilix": DITILIX_SIZES}[design]
     for name in design_sizes:
         lan = named_config_json(name)
         if args.layers:
@@ -909,7 +1069,9 @@ def run_design(args):
         per_seq = -(-(args.prompt_len + warmup + steps + 2) // 64) * 64
         max_tokens = max(args.batch * per_seq, PREFILL_TOKENS + 64) + 64
         entry = {"layers": [l["type"] for l in lan["layers"]], "width": lan["width"]}
-        beside = ("qwen3_same_size", qwen3_like(lan)) if design == "lanilix" else ("lanilix_same_size", lanilix_like(lan))
+        beside = {"lanilix": lambda: ("qwen3_same_size", qwen3_like(lan)),
+                  "bunudra": lambda: ("lanilix_same_size", lanilix_like(lan)),
+                  "ditilix": lambda: ("qwen3_same_size", qwen3_like_ditilix(lan))}[design]()
         for label, data in ((design, lan), beside):
             engine = Engine.from_config(config_from_dict(data), seed=0, dtype="bfloat16", max_tokens=max_tokens,
                                         max_batch=args.batch)
@@ -917,7 +1079,7 @@ def run_design(args):
                                          args.prompt_len, steps, warmup)
             del engine
             torch.cuda.empty_cache()
-        table = kernel_table if design == "lanilix" else bunudra_kernel_table
+        table = {"lanilix": kernel_table, "bunudra": bunudra_kernel_table, "ditilix": ditilix_kernel_table}[design]
         entry["kernels"] = table(torch, lan, peak, args.batch, args.prompt_len)
         sizes[name] = entry
     clocks = sampler.stop()
@@ -1132,9 +1294,10 @@ def main():
                              "(for ncu --profile-from-start off)")
     parser.add_argument("--workload", choices=sorted(LARGE_WORKLOADS), default=None,
                         help="one of the two larger workloads instead of the default run")
-    parser.add_argument("--design", choices=["lanilix", "bunudra"], default=None,
+    parser.add_argument("--design", choices=["lanilix", "bunudra", "ditilix"], default=None,
                         help="another design beside its closest relative at the same sizes (Lanilix beside Qwen3, "
-                             "Bunudra beside Lanilix), model by model and kernel by kernel, instead of the default run")
+                             "Bunudra beside Lanilix, Ditilix beside Qwen3), model by model and kernel by kernel, "
+                             "instead of the default run")
     args = parser.parse_args()
     args.steps_given = args.steps is not None
     if args.steps is None:

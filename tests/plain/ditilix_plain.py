@@ -186,13 +186,17 @@ def route(z, top):
     return chosen, s.gather(-1, chosen)
 
 
-def moe(n, t, prefix, mlp, ar):
+def moe(n, t, prefix, mlp, ar, margins=None):
     """The chosen experts see the token times its routing weight; their outputs are summed as
     they are.  The shared expert sees the token itself; its output is multiplied by
-    ``logistic(sg . n)``."""
+    ``logistic(sg . n)``.  ``margins`` (a list) receives, per token, the distance in the router's
+    logits between the last expert chosen and the first one left out."""
     router = mlp["router"]
     z = ar.linear(n, t[prefix + "router"], keep=True)
     chosen, weights = route(z, int(router["top"]))
+    if margins is not None and int(router["top"]) < int(router["experts"]):
+        ordered = z.sort(dim=-1, descending=True).values
+        margins.append(ordered[:, int(router["top"]) - 1] - ordered[:, int(router["top"])])
     out = torch.zeros_like(n)
     limit = float(mlp["expert"]["limit"])
     for e in range(int(router["experts"])):
@@ -206,18 +210,18 @@ def moe(n, t, prefix, mlp, ar):
     return out
 
 
-def feed_forward(n, t, prefix, mlp, eps, ar):
+def feed_forward(n, t, prefix, mlp, eps, ar, margins=None):
     if mlp["kind"] == "dense":
         return dense_ff(n, t, prefix, eps, ar)
-    return moe(n, t, prefix, mlp, ar)
+    return moe(n, t, prefix, mlp, ar, margins)
 
 
 # ----------------------------------------------------------------------------- the model
 
 
-def forward(config, tensors, tokens, precision=torch.float64, layers_out=None):
+def forward(config, tensors, tokens, precision=torch.float64, layers_out=None, margins=None):
     """Logits [T, vocab] of one whole sequence; ``layers_out`` (a list) receives the stream after
-    every layer."""
+    every layer, ``margins`` (a list) the routing margins [T] of every routed layer."""
     ar = Arithmetic(precision)
     w = ar.work
     t = {k: v.to(w) if v.is_floating_point() else v for k, v in tensors.items()}
@@ -237,7 +241,7 @@ def forward(config, tensors, tokens, precision=torch.float64, layers_out=None):
             kv = held[int(m["kv_from"])]
         y = attention_mixer(n, t, p + "mix.", m, ar, kv)
         if layer.get("mlp"):
-            y = y + feed_forward(n, t, p + "mlp.", layer["mlp"], eps, ar)
+            y = y + feed_forward(n, t, p + "mlp.", layer["mlp"], eps, ar, margins)
         x = x + r * y
         if layers_out is not None:
             layers_out.append(x.clone())
@@ -250,6 +254,17 @@ def greedy(config, tensors, prompt, n_new, precision=torch.float64):
     for _ in range(n_new):
         out.append(int(forward(config, tensors, out, precision)[-1].argmax()))
     return out[len(prompt):]
+
+
+def routing_margin(config, tensors, tokens):
+    """[T]: per token, the smallest routing margin over the routed layers, in exact arithmetic
+    (infinite where every expert is chosen)."""
+    margins = []
+    forward(config, tensors, tokens, torch.float64, margins=margins)
+    out = torch.full((len(tokens),), float("inf"), dtype=torch.float64)
+    for m in margins:
+        out = torch.minimum(out, m)
+    return out
 
 
 _models = {}
