@@ -945,7 +945,7 @@ def ditilix_kernel_table(torch, dit, peak, batch, context):
     def row(name, fn, nbytes=0, flops=0, like=None):
         us = timed(fn)
         t_roof = max(nbytes / hbm, flops / tensor) * 1e6
-        rows[name] = {"us": round(us, 2), "roofline_us": round(t_roof, 2), "frac": round(t_roof / us, 3), "like": like,
+        rows[name] = {"us": round(us, 2), "roofline_us": round(t_roof, 3), "frac": round(t_roof / us, 5), "like": like,
                       "bound": "hbm" if nbytes / hbm >= flops / tensor else "flops"}
 
     g = torch.Generator(device=dev).manual_seed(0)
@@ -1044,7 +1044,7 @@ def ditilix_kernel_table(torch, dit, peak, batch, context):
                    shaped, tuple(f"{t}: {x}" for t in ("prefill", "decode") for x in qwen_tags))
     ops.raise_on_device_error(err, "kernel table")
     for name, r in rows.items():
-        if r["like"] in rows:
+        if r["like"] in rows and r["frac"] > 0:
             r["times_farther_than_like"] = round(rows[r["like"]]["frac"] / r["frac"], 2)
     return rows
 

@@ -116,7 +116,7 @@ def close(got, want, dtype, what):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("width, groups", [(48, 1), (48, 4), (100, 5), (30, 30), (4096, 8), (5000, 2)])
+@pytest.mark.parametrize("width, groups", [(48, 1), (48, 4), (100, 5), (30, 30), (4096, 8), (5000, 2), (12288, 1), (12288, 8), (12200, 4)])
 def test_grouped_norm_over_a_stream_that_takes_two_branches_and_a_factor(dtype, width, groups):
     from thing_htn_2026_b200 import ops
     t = TORCH[dtype]
@@ -159,7 +159,7 @@ def test_sinusoidal_positions_on_the_rows_of_the_embedding(width):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("width", [3, 64, 77, 1000, 6000])
+@pytest.mark.parametrize("width", [3, 64, 77, 1000, 6000, 12288, 12250, 20000])
 def test_polynomial_of_norms_alone(dtype, width):
     from thing_htn_2026_b200 import ops
     t = TORCH[dtype]

@@ -87,6 +87,20 @@ def test_gemm_f32_is_true_float32(m, n, k):
     assert torch.equal(alone[0], out[0])
 
 
+@pytest.mark.parametrize("m, n, k", [(1, 1, 8), (7, 9, 72), (64, 9, 2048), (300, 33, 4104), (2100, 5, 1024), (3, 64, 96)])
+def test_a_few_float32_outputs_per_row(m, n, k):
+    """The product that routers and gates take (bfloat16 operands, float32 result, few columns):
+    exact sums of the bfloat16 products up to float32 rounding, and a row's result does not
+    depend on the rows beside it."""
+    x, w = rand((m, k), torch.bfloat16, 1), rand((n, k), torch.bfloat16, 2, 0.3)
+    got = ops().linear(x.to(DEV), w.to(DEV), out_dtype=torch.float32)
+    assert got.dtype == torch.float32 and tuple(got.shape) == (m, n)
+    want = x.double() @ w.double().t()
+    assert (got.cpu().double() - want).abs().max() <= 2e-6 * max(1.0, want.abs().max().item()) * (k ** 0.5)
+    alone = ops().linear(x[m // 2:m // 2 + 1].to(DEV).contiguous(), w.to(DEV), out_dtype=torch.float32)
+    assert torch.equal(alone[0], got[m // 2])
+
+
 def test_rope_table_matches_formula():
     from thing_htn_2026_b200.config.base import PartSpec
     from thing_htn_2026_b200.parts import Runtime, part_class

@@ -461,12 +461,12 @@ void launch_recurrence(float* o, float* state, const float* qn, const float* kn,
     constexpr size_t smem = recurrence_smem<R, L, W>();
     dim3 grid(n_seqs, s.n_heads, (s.dv + kCols - 1) / kCols);
     if (carry_double) {
-        if (smem > 48 * 1024)
+        if (smem > 32 * 1024)
             cudaFuncSetAttribute(delta_recurrence_kernel<R, VEC, L, W, double>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         thn_launch_ordered(delta_recurrence_kernel<R, VEC, L, W, double>, grid, W * 32, smem, stream, o, state, qn, kn, vc, beta,
                    decay, cu, slots, s);
     } else {
-        if (smem > 48 * 1024)
+        if (smem > 32 * 1024)
             cudaFuncSetAttribute(delta_recurrence_kernel<R, VEC, L, W, float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         thn_launch_ordered(delta_recurrence_kernel<R, VEC, L, W, float>, grid, W * 32, smem, stream, o, state, qn, kn, vc, beta,
                    decay, cu, slots, s);

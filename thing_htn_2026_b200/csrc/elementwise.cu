@@ -491,13 +491,38 @@ THN_API int thn_clamped_glu(void* out, const void* gu, int rows, int inter, floa
 // N(v) = v / sqrt(mean(v^2) + eps) over the row; (a, b, c, e) = coef[0..3].  One block per row,
 // the row staged in shared memory; the three sums of squares are float32 and their order depends
 // on the block size only; one rounding at the store.
+// Three sums over a block at once; every thread gets all three.  The order of additions depends
+// only on blockDim.
+__device__ __forceinline__ void block_sum3(float& a, float& b, float& c, float (*scratch)[33]) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    a = warp_sum(a);
+    b = warp_sum(b);
+    c = warp_sum(c);
+    if (lane == 0) {
+        scratch[0][warp] = a;
+        scratch[1][warp] = b;
+        scratch[2][warp] = c;
+    }
+    __syncthreads();
+    if (warp < 3) {
+        const int n_warps = (blockDim.x + 31) >> 5;
+        float t = lane < n_warps ? scratch[warp][lane] : 0.f;
+        t = warp_sum(t);
+        if (lane == 0) scratch[warp][32] = t;
+    }
+    __syncthreads();
+    a = scratch[0][32];
+    b = scratch[1][32];
+    c = scratch[2][32];
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256) polynorm_kernel(T* __restrict__ out, const T* __restrict__ z,
                                                        const float* __restrict__ coef, int width, float eps) {
     pdl_launch_dependents();
     pdl_wait();
     extern __shared__ float poly_row[];
-    __shared__ float scratch[33];
+    __shared__ float scratch[3][33];
     const size_t base = (size_t)blockIdx.x * width;
     float s1 = 0.f, s2 = 0.f, s3 = 0.f;
     for (int i = threadIdx.x; i < width; i += blockDim.x) {
@@ -508,14 +533,65 @@ __global__ void __launch_bounds__(256) polynorm_kernel(T* __restrict__ out, cons
         s2 += v2 * v2;
         s3 += v2 * v2 * v2;
     }
+    block_sum3(s1, s2, s3, scratch);
     const float n = (float)width;
-    const float r1 = coef[0] / sqrtf(block_sum(s1, scratch) / n + eps);
-    const float r2 = coef[1] / sqrtf(block_sum(s2, scratch) / n + eps);
-    const float r3 = coef[2] / sqrtf(block_sum(s3, scratch) / n + eps);
+    const float r1 = coef[0] / sqrtf(s1 / n + eps);
+    const float r2 = coef[1] / sqrtf(s2 / n + eps);
+    const float r3 = coef[2] / sqrtf(s3 / n + eps);
     const float shift = coef[3];
     for (int i = threadIdx.x; i < width; i += blockDim.x) {
         const float v = poly_row[i];
         out[base + i] = from_f32<T>(v * (r1 + v * (r2 + v * r3)) + shift);
+    }
+}
+
+// The same for bfloat16 rows of a multiple of eight values at 16-byte aligned addresses: 16-byte
+// accesses, the row staged as it was read.
+template <int THREADS>
+__global__ void __launch_bounds__(THREADS) polynorm_bf16x8_kernel(__nv_bfloat16* __restrict__ out,
+                                                                  const __nv_bfloat16* __restrict__ z,
+                                                                  const float* __restrict__ coef, int vecs, float eps) {
+    pdl_launch_dependents();
+    pdl_wait();
+    extern __shared__ uint4 poly_vecs[];
+    __shared__ float scratch[3][33];
+    const uint4* src = reinterpret_cast<const uint4*>(z) + (size_t)blockIdx.x * vecs;
+    uint4* dst = reinterpret_cast<uint4*>(out) + (size_t)blockIdx.x * vecs;
+    float s1 = 0.f, s2 = 0.f, s3 = 0.f;
+    for (int i = threadIdx.x; i < vecs; i += THREADS) {
+        const uint4 raw = src[i];
+        poly_vecs[i] = raw;
+        const __nv_bfloat162* pairs = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float2 v = __bfloat1622float2(pairs[k]);
+            const float a = v.x * v.x, b = v.y * v.y;
+            s1 += a;
+            s2 += a * a;
+            s3 += a * a * a;
+            s1 += b;
+            s2 += b * b;
+            s3 += b * b * b;
+        }
+    }
+    block_sum3(s1, s2, s3, scratch);
+    const float n = 8.f * (float)vecs;
+    const float r1 = coef[0] / sqrtf(s1 / n + eps);
+    const float r2 = coef[1] / sqrtf(s2 / n + eps);
+    const float r3 = coef[2] / sqrtf(s3 / n + eps);
+    const float shift = coef[3];
+    for (int i = threadIdx.x; i < vecs; i += THREADS) {
+        const uint4 raw = poly_vecs[i];
+        const __nv_bfloat162* pairs = reinterpret_cast<const __nv_bfloat162*>(&raw);
+        uint4 res;
+        __nv_bfloat162* o = reinterpret_cast<__nv_bfloat162*>(&res);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float2 v = __bfloat1622float2(pairs[k]);
+            o[k] = __floats2bfloat162_rn(v.x * (r1 + v.x * (r2 + v.x * r3)) + shift,
+                                         v.y * (r1 + v.y * (r2 + v.y * r3)) + shift);
+        }
+        dst[i] = res;
     }
 }
 
@@ -527,13 +603,25 @@ THN_API int thn_polynorm(void* out, const void* z, const float* coef, int rows, 
     const size_t smem = (size_t)width * sizeof(float);
     THN_UNSUPPORTED_IF(smem > 200 * 1024, "polynorm: rows of %d values do not fit shared memory", width);
     if (dtype == THN_F32) {
-        if (smem > 48 * 1024) cudaFuncSetAttribute(polynorm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (smem > 32 * 1024) cudaFuncSetAttribute(polynorm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         thn_launch(polynorm_kernel<float>, rows, 256, smem, stream, (float*)out, (const float*)z, coef, width, eps);
     } else if (dtype == THN_BF16) {
-        if (smem > 48 * 1024)
-            cudaFuncSetAttribute(polynorm_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        thn_launch(polynorm_kernel<__nv_bfloat16>, rows, 256, smem, stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)z, coef,
-                   width, eps);
+        const bool aligned = width % 8 == 0 && ((uintptr_t)out | (uintptr_t)z) % 16 == 0;
+        if (aligned && width >= 8192) {          // the choice depends on the row's size only
+            const size_t staged = (size_t)width * sizeof(__nv_bfloat16);
+            if (staged > 32 * 1024)
+                cudaFuncSetAttribute(polynorm_bf16x8_kernel<512>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)staged);
+            thn_launch(polynorm_bf16x8_kernel<512>, rows, 512, staged, stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)z,
+                       coef, width / 8, eps);
+        } else if (aligned) {
+            thn_launch(polynorm_bf16x8_kernel<256>, rows, 256, (size_t)width * sizeof(__nv_bfloat16), stream,
+                       (__nv_bfloat16*)out, (const __nv_bfloat16*)z, coef, width / 8, eps);
+        } else {
+            if (smem > 32 * 1024)
+                cudaFuncSetAttribute(polynorm_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            thn_launch(polynorm_kernel<__nv_bfloat16>, rows, 256, smem, stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)z,
+                       coef, width, eps);
+        }
     } else {
         THN_CHECK_ARG(false, "polynorm: unknown dtype %d", dtype);
     }

@@ -67,3 +67,67 @@ THN_API int thn_gemm_f32(float* C, const float* A, const float* W, int M, int N,
     thn_launch(gemm_f32_kernel, grid, 256, 0, stream, C, A, W, M, N, K);
     return thn_launch_status("gemm_f32");
 }
+
+// ------------------------------------------------------------------ a few outputs per row, float32 out
+//
+// C[M, N] float32 = A[M, K] bfloat16 @ W[N, K]^T bfloat16 for a weight of few rows (a router, a
+// gate of one number per token): the products that vendor libraries serve worst, since N is
+// neither large nor a multiple of eight.  One warp per row of A: the row's 16-byte pieces stay in
+// the L1 cache while the warp walks the outputs four at a time; every lane accumulates its
+// pieces k = lane, lane + 32, ... in float32 and the lanes are summed by shuffles, so a row's
+// result depends on nothing but K.  K is a multiple of eight and both operands are 16-byte
+// aligned.
+namespace {
+constexpr int kSkinnyWarps = 8;
+
+__device__ __forceinline__ float dot8(const uint4& a, const uint4& b, float acc) {
+    const __nv_bfloat162* x = reinterpret_cast<const __nv_bfloat162*>(&a);
+    const __nv_bfloat162* y = reinterpret_cast<const __nv_bfloat162*>(&b);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 u = __bfloat1622float2(x[i]), v = __bfloat1622float2(y[i]);
+        acc = fmaf(u.x, v.x, acc);
+        acc = fmaf(u.y, v.y, acc);
+    }
+    return acc;
+}
+
+__global__ void __launch_bounds__(kSkinnyWarps * 32) linear_skinny_kernel(float* __restrict__ C,
+                                                                          const __nv_bfloat16* __restrict__ A,
+                                                                          const __nv_bfloat16* __restrict__ W, int M, int N,
+                                                                          int vecs) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const int m = blockIdx.x * kSkinnyWarps + (threadIdx.x >> 5);
+    if (m >= M) return;
+    const uint4* a = reinterpret_cast<const uint4*>(A) + (size_t)m * vecs;
+    const uint4* w = reinterpret_cast<const uint4*>(W);
+    for (int n0 = 0; n0 < N; n0 += 4) {
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+        const int live = min(4, N - n0);
+        for (int i = lane; i < vecs; i += 32) {
+            const uint4 av = a[i];
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                if (j < live) acc[j] = dot8(av, __ldg(w + (size_t)(n0 + j) * vecs + i), acc[j]);
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float total = warp_sum(acc[j]);
+            if (j < live && lane == 0) C[(size_t)m * N + n0 + j] = total;
+        }
+    }
+}
+}  // namespace
+
+THN_API int thn_linear_skinny_supported(int N, int K) { return N >= 1 && N <= 64 && K >= 8 && K % 8 == 0; }
+
+THN_API int thn_linear_skinny_bf16(float* C, const void* A, const void* W, int M, int N, int K, cudaStream_t stream) {
+    THN_CHECK_ARG(M >= 0 && thn_linear_skinny_supported(N, K), "linear_skinny: bad sizes M=%d N=%d K=%d", M, N, K);
+    THN_CHECK_ARG((((uintptr_t)A | (uintptr_t)W) & 15) == 0, "linear_skinny: operands must be 16-byte aligned (M=%d)", M);
+    if (M == 0) return THN_OK;
+    thn_launch(linear_skinny_kernel, (M + kSkinnyWarps - 1) / kSkinnyWarps, kSkinnyWarps * 32, 0, stream, C,
+               (const __nv_bfloat16*)A, (const __nv_bfloat16*)W, M, N, K / 8);
+    return thn_launch_status("linear_skinny");
+}

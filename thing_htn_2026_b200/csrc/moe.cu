@@ -277,7 +277,7 @@ THN_API int thn_moe_route(float* dense, int* chosen, float* chosen_weight, const
     THN_UNSUPPORTED_IF(n_experts > 4096, "moe_route: %d experts, at most 4096", n_experts);
     if (n_rows == 0) return THN_OK;
     const size_t smem = (size_t)kRouteWarps * (n_experts + n_groups) * sizeof(float);
-    if (smem > 48 * 1024)
+    if (smem > 32 * 1024)
         cudaFuncSetAttribute(moe_route_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     thn_launch(moe_route_kernel, (n_rows + kRouteWarps - 1) / kRouteWarps, kRouteWarps * 32, smem, stream, dense, chosen,
                chosen_weight, z, z_stride, n_rows, n_experts, n_groups, keep, top, scale, scoring);

@@ -122,7 +122,7 @@ template <typename T>
 int launch(void* y, float* h, const void* d, const void* d2, float mult, NormArgs post, NormArgs out, int rows, int width,
            int h_is_new, cudaStream_t stream) {
     const size_t smem = (size_t)(width + (out.groups > 1 ? out.groups : 0)) * sizeof(float);
-    if (smem > 48 * 1024) {
+    if (smem > 32 * 1024) {
         THN_UNSUPPORTED_IF(smem > 200 * 1024, "residual_norm: rows of %d values do not fit shared memory", width);
         cudaFuncSetAttribute(residual_norm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     }

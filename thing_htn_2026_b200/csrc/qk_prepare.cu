@@ -262,7 +262,7 @@ int launch(void* q_out, const void* proj, int proj_width, const float* q_gain, c
     const bool pairs = D % 2 == 0 && kv.value_dim % 2 == 0 && proj_width % 2 == 0 && (interleaved || (rotary_dim / 2) % 2 == 0) &&
                        (((uintptr_t)proj | (uintptr_t)q_out | (uintptr_t)kv.base) & (2 * sizeof(T) - 1)) == 0;
     if (!pairs) {
-        if (smem > 48 * 1024)
+        if (smem > 32 * 1024)
             cudaFuncSetAttribute(qk_prepare_scalar_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         thn_launch(qk_prepare_scalar_kernel<T>, n_rows, 128, smem, stream, (T*)q_out, (const T*)proj, proj_width, q_gain,
                    k_gain, norm_scope, gain_offset, eps, cos_tab, sin_tab, table_len, rotary_dim, interleaved,
@@ -275,7 +275,7 @@ int launch(void* q_out, const void* proj, int proj_width, const float* q_gain, c
     // and more blocks per SM, 256 for rows of 4,096 entries or more
 #define THN_QK_LAUNCH(THREADS)                                                                                        \
     do {                                                                                                              \
-        if (smem > 48 * 1024)                                                                                         \
+        if (smem > 32 * 1024)                                                                                         \
             cudaFuncSetAttribute(qk_prepare_kernel<T, THREADS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
         thn_launch(qk_prepare_kernel<T, THREADS>, n_rows, THREADS, smem, stream, (T*)q_out, (const T*)proj, proj_width, \
                    q_gain, k_gain, norm_scope, gain_offset, eps, cos_tab, sin_tab, table_len, rotary_dim, interleaved, \

@@ -93,6 +93,8 @@ _SIGNATURES = {
     "thn_delta_decode": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                          c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
     "thn_gemm_f32": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "thn_linear_skinny_bf16": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "thn_linear_skinny_supported": [c_int, c_int],
     "thn_scatter_i32": [c_void_p, c_void_p, c_void_p, c_int, c_longlong, c_void_p],
     "thn_choose_tokens": [c_void_p, c_void_p, c_int, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p,
                           c_void_p, c_void_p, c_int, c_void_p, c_void_p],
@@ -622,7 +624,8 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtyp
            err: Optional[torch.Tensor] = None) -> torch.Tensor:
     """x [M, K] @ weight[N, K]^T.  float32: this library's FFMA kernel.  bfloat16 with few
     rows and a deep reduction or a tall weight: this library's weight-streaming kernel
-    (``err``: the step's device error word for its bounded waits).  bfloat16 otherwise: the
+    (``err``: the step's device error word for its bounded waits).  bfloat16 with a float32 result
+    of at most 64 columns (a router, a gate): this library's warp-per-row kernel.  bfloat16 otherwise: the
     vendor library's tensor-core product with float32 accumulation (the reference's choice,
     engine/engine.py:341-350).  ``out_dtype=torch.float32`` keeps the accumulator's
     precision (used for logits)."""
@@ -636,6 +639,12 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtyp
         return out
     if x.dtype != torch.bfloat16:
         raise KernelError(f"linear: dtype {x.dtype} is not supported")
+    if (out_dtype == torch.float32 and lib().thn_linear_skinny_supported(weight.shape[0], x.shape[1])
+            and (x.data_ptr() | weight.data_ptr()) % 16 == 0):
+        # a router or a gate: a few float32 outputs per row, on this library's warp-per-row kernel
+        out = torch.empty((x.shape[0], weight.shape[0]), dtype=torch.float32, device=x.device)
+        _call("thn_linear_skinny_bf16", _ptr(out), _ptr(x), _ptr(weight), x.shape[0], weight.shape[0], x.shape[1], _stream())
+        return out
     if _stream_takes(x.shape[0], weight.shape[0], x.shape[1]):
         return linear_stream(x, weight, out_dtype or torch.bfloat16, err=err)
     if out_dtype in (None, torch.bfloat16):
