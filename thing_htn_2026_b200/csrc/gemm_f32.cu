@@ -72,13 +72,13 @@ THN_API int thn_gemm_f32(float* C, const float* A, const float* W, int M, int N,
 //
 // C[M, N] float32 = A[M, K] bfloat16 @ W[N, K]^T bfloat16 for a weight of few rows (a router, a
 // gate of one number per token): the products that vendor libraries serve worst, since N is
-// neither large nor a multiple of eight.  One warp per row of A: the row's 16-byte pieces stay in
-// the L1 cache while the warp walks the outputs four at a time; every lane accumulates its
-// pieces k = lane, lane + 32, ... in float32 and the lanes are summed by shuffles, so a row's
-// result depends on nothing but K.  K is a multiple of eight and both operands are 16-byte
-// aligned.
+// neither large nor a multiple of eight.  A block of eight warps takes ROWS rows of A and walks
+// the outputs four at a time: a thread's 16-byte pieces k = t, t + 256, ... of the rows and of
+// four weight rows are loaded side by side (one round trip to memory), multiplied in float32,
+// summed over the warp by shuffles and over the warps in a fixed order.  A row's result depends on
+// nothing but K, whatever ROWS is.  K is a multiple of eight and both operands are 16-byte aligned.
 namespace {
-constexpr int kSkinnyWarps = 8;
+constexpr int kSkinnyThreads = 256;
 
 __device__ __forceinline__ float dot8(const uint4& a, const uint4& b, float acc) {
     const __nv_bfloat162* x = reinterpret_cast<const __nv_bfloat162*>(&a);
@@ -92,31 +92,52 @@ __device__ __forceinline__ float dot8(const uint4& a, const uint4& b, float acc)
     return acc;
 }
 
-__global__ void __launch_bounds__(kSkinnyWarps * 32) linear_skinny_kernel(float* __restrict__ C,
-                                                                          const __nv_bfloat16* __restrict__ A,
-                                                                          const __nv_bfloat16* __restrict__ W, int M, int N,
-                                                                          int vecs) {
+template <int ROWS>
+__global__ void __launch_bounds__(kSkinnyThreads) linear_skinny_kernel(float* __restrict__ C,
+                                                                       const __nv_bfloat16* __restrict__ A,
+                                                                       const __nv_bfloat16* __restrict__ W, int M, int N,
+                                                                       int vecs) {
     pdl_launch_dependents();
     pdl_wait();
-    const int lane = threadIdx.x & 31;
-    const int m = blockIdx.x * kSkinnyWarps + (threadIdx.x >> 5);
-    if (m >= M) return;
-    const uint4* a = reinterpret_cast<const uint4*>(A) + (size_t)m * vecs;
+    __shared__ float part[kSkinnyThreads / 32][ROWS * 4];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int m0 = blockIdx.x * ROWS;
+    const uint4* a = reinterpret_cast<const uint4*>(A);
     const uint4* w = reinterpret_cast<const uint4*>(W);
+    const uint4 zero = make_uint4(0, 0, 0, 0);
     for (int n0 = 0; n0 < N; n0 += 4) {
-        float acc[4] = {0.f, 0.f, 0.f, 0.f};
-        const int live = min(4, N - n0);
-        for (int i = lane; i < vecs; i += 32) {
-            const uint4 av = a[i];
+        float acc[ROWS][4];
 #pragma unroll
-            for (int j = 0; j < 4; ++j)
-                if (j < live) acc[j] = dot8(av, __ldg(w + (size_t)(n0 + j) * vecs + i), acc[j]);
+        for (int r = 0; r < ROWS; ++r)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) acc[r][j] = 0.f;
+        for (int i = threadIdx.x; i < vecs; i += kSkinnyThreads) {
+            uint4 av[ROWS], wv[4];
+#pragma unroll
+            for (int r = 0; r < ROWS; ++r) av[r] = m0 + r < M ? a[(size_t)(m0 + r) * vecs + i] : zero;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) wv[j] = n0 + j < N ? __ldg(w + (size_t)(n0 + j) * vecs + i) : zero;
+#pragma unroll
+            for (int r = 0; r < ROWS; ++r)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[r][j] = dot8(av[r], wv[j], acc[r][j]);
         }
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const float total = warp_sum(acc[j]);
-            if (j < live && lane == 0) C[(size_t)m * N + n0 + j] = total;
+        for (int r = 0; r < ROWS; ++r)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float total = warp_sum(acc[r][j]);
+                if (lane == 0) part[warp][r * 4 + j] = total;
+            }
+        __syncthreads();
+        if (threadIdx.x < ROWS * 4) {
+            const int r = threadIdx.x >> 2, j = threadIdx.x & 3;
+            float total = 0.f;
+#pragma unroll
+            for (int k = 0; k < kSkinnyThreads / 32; ++k) total += part[k][threadIdx.x];
+            if (m0 + r < M && n0 + j < N) C[(size_t)(m0 + r) * N + n0 + j] = total;
         }
+        __syncthreads();
     }
 }
 }  // namespace
@@ -127,7 +148,11 @@ THN_API int thn_linear_skinny_bf16(float* C, const void* A, const void* W, int M
     THN_CHECK_ARG(M >= 0 && thn_linear_skinny_supported(N, K), "linear_skinny: bad sizes M=%d N=%d K=%d", M, N, K);
     THN_CHECK_ARG((((uintptr_t)A | (uintptr_t)W) & 15) == 0, "linear_skinny: operands must be 16-byte aligned (M=%d)", M);
     if (M == 0) return THN_OK;
-    thn_launch(linear_skinny_kernel, (M + kSkinnyWarps - 1) / kSkinnyWarps, kSkinnyWarps * 32, 0, stream, C,
-               (const __nv_bfloat16*)A, (const __nv_bfloat16*)W, M, N, K / 8);
+    if (M >= 1024)      // enough rows to fill the SMs four at a time: the weight's rows are read a quarter as often
+        thn_launch(linear_skinny_kernel<4>, (M + 3) / 4, kSkinnyThreads, 0, stream, C, (const __nv_bfloat16*)A,
+                   (const __nv_bfloat16*)W, M, N, K / 8);
+    else
+        thn_launch(linear_skinny_kernel<1>, M, kSkinnyThreads, 0, stream, C, (const __nv_bfloat16*)A,
+                   (const __nv_bfloat16*)W, M, N, K / 8);
     return thn_launch_status("linear_skinny");
 }
