@@ -18,6 +18,8 @@
 // float32; y is rounded once to the activation type T.  One block per row, the row staged in
 // shared memory; the order of additions depends on the block size only, so a row's result does
 // not depend on its batch.
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace {
@@ -118,14 +120,141 @@ __global__ void __launch_bounds__(kThreads) residual_norm_kernel(
     }
 }
 
+// The same for bfloat16 activations, rows of a multiple of eight values and 16-byte aligned
+// operands: every access to global memory moves eight values (16 bytes of bfloat16, two 16-byte
+// pieces of float32).  The staged row, the statistics and every formula are those of the kernel
+// above, so the two give the same bits.
+__device__ __forceinline__ void load8(const float* p, float (&v)[8]) {
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    v[0] = a.x, v[1] = a.y, v[2] = a.z, v[3] = a.w, v[4] = b.x, v[5] = b.y, v[6] = b.z, v[7] = b.w;
+}
+__device__ __forceinline__ void store8(float* p, const float (&v)[8]) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+}
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&v)[8]) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* pairs = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const float2 f = __bfloat1622float2(pairs[k]);
+        v[2 * k] = f.x, v[2 * k + 1] = f.y;
+    }
+}
+__device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&v)[8]) {
+    uint4 raw;
+    __nv_bfloat162* pairs = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) pairs[k] = __floats2bfloat162_rn(v[2 * k], v[2 * k + 1]);
+    *reinterpret_cast<uint4*>(p) = raw;
+}
+
+__global__ void __launch_bounds__(kThreads) residual_norm_bf16x8_kernel(
+    __nv_bfloat16* __restrict__ y, float* __restrict__ h, const __nv_bfloat16* __restrict__ d,
+    const __nv_bfloat16* __restrict__ d2, float mult, NormArgs post, NormArgs out, int width, int h_is_new) {
+    pdl_launch_dependents();
+    pdl_wait();
+    extern __shared__ __align__(16) float row[];
+    __shared__ float scratch[33];
+    const size_t base = (size_t)blockIdx.x * width;
+    float v[8], u[8];
+    if (d) {
+        if (post.kind) {
+            for (int i = threadIdx.x * 8; i < width; i += kThreads * 8) {
+                load8(d + base + i, v);
+                if (d2) {
+                    load8(d2 + base + i, u);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) v[e] += u[e];
+                }
+                store8(row + i, v);
+            }
+            __syncthreads();
+        }
+        float2 st = make_float2(0.f, 1.f);
+        if (post.kind) st = row_statistics(row, width, post.kind, post.eps, scratch);
+        for (int i = threadIdx.x * 8; i < width; i += kThreads * 8) {
+            if (post.kind) {
+                load8(row + i, v);
+                load8(post.gain + i, u);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) v[e] = (v[e] - st.x) * st.y * (post.offset + u[e]);
+                if (post.bias) {
+                    load8(post.bias + i, u);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) v[e] += u[e];
+                }
+            } else {
+                load8(d + base + i, v);
+                if (d2) {
+                    load8(d2 + base + i, u);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) v[e] += u[e];
+                }
+            }
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[e] *= mult;
+            if (!h_is_new) {
+                load8(h + base + i, u);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) v[e] = u[e] + v[e];
+            }
+            store8(h + base + i, v);
+            store8(row + i, v);
+        }
+    } else {
+        for (int i = threadIdx.x * 8; i < width; i += kThreads * 8) {
+            load8(h + base + i, v);
+            store8(row + i, v);
+        }
+    }
+    if (!out.kind) return;
+    if (out.kind == 3) {
+        for (int i = threadIdx.x * 8; i < width; i += kThreads * 8) {
+            load8(row + i, v);          // the thread's own pieces: no barrier needed
+            store8(y + base + i, v);
+        }
+        return;
+    }
+    __syncthreads();
+    const bool grouped = out.kind == 1 && out.groups > 1;
+    float* rstd = row + width;
+    float2 st = make_float2(0.f, 1.f);
+    if (grouped) group_statistics(row, width, out.groups, out.eps, rstd);
+    else st = row_statistics(row, width, out.kind, out.eps, scratch);
+    const int per = width / out.groups;
+    for (int i = threadIdx.x * 8; i < width; i += kThreads * 8) {
+        load8(row + i, v);
+        load8(out.gain + i, u);
+#pragma unroll
+        for (int e = 0; e < 8; ++e)
+            v[e] = grouped ? v[e] * rstd[(i + e) / per] * (out.offset + u[e]) : (v[e] - st.x) * st.y * (out.offset + u[e]);
+        if (out.bias) {
+            load8(out.bias + i, u);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[e] += u[e];
+        }
+        store8(y + base + i, v);
+    }
+}
+
+inline bool aligned16(const void* p) { return ((uintptr_t)p & 15) == 0; }
+
 template <typename T>
 int launch(void* y, float* h, const void* d, const void* d2, float mult, NormArgs post, NormArgs out, int rows, int width,
            int h_is_new, cudaStream_t stream) {
     const size_t smem = (size_t)(width + (out.groups > 1 ? out.groups : 0)) * sizeof(float);
-    if (smem > 32 * 1024) {
-        THN_UNSUPPORTED_IF(smem > 200 * 1024, "residual_norm: rows of %d values do not fit shared memory", width);
-        cudaFuncSetAttribute(residual_norm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    THN_UNSUPPORTED_IF(smem > 200 * 1024, "residual_norm: rows of %d values do not fit shared memory", width);
+    if (std::is_same<T, __nv_bfloat16>::value && width % 8 == 0 && aligned16(y) && aligned16(h) && aligned16(d) &&
+        aligned16(d2) && aligned16(post.gain) && aligned16(post.bias) && aligned16(out.gain) && aligned16(out.bias)) {
+        if (smem > 32 * 1024)
+            cudaFuncSetAttribute(residual_norm_bf16x8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        thn_launch(residual_norm_bf16x8_kernel, rows, kThreads, smem, stream, (__nv_bfloat16*)y, h, (const __nv_bfloat16*)d,
+                   (const __nv_bfloat16*)d2, mult, post, out, width, h_is_new);
+        return thn_launch_status("residual_norm");
     }
+    if (smem > 32 * 1024)
+        cudaFuncSetAttribute(residual_norm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     thn_launch(residual_norm_kernel<T>, rows, kThreads, smem, stream, (T*)y, h, (const T*)d, (const T*)d2, mult, post, out, width, h_is_new);
     return thn_launch_status("residual_norm");
 }
