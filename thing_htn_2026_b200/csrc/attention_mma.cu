@@ -867,7 +867,7 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 }
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
     const uint32_t addr = smem_u32(bar);
-    unsigned long long start = 0;
+    WaitClock clock;
     for (;;) {
         uint32_t done;
         asm volatile(
@@ -880,10 +880,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
             : "r"(addr), "r"(parity)
             : "memory");
         if (done) return true;
-        unsigned long long now;
-        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
-        if (start == 0) start = now;
-        else if (now - start > kStreamWaitNs) return false;
+        if (clock.ran_out(kStreamWaitNs)) return false;
     }
 }
 __device__ __forceinline__ void tma_tile(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {

@@ -59,7 +59,7 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 // the whole wait.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
     const uint32_t addr = smem_addr(bar);
-    unsigned long long start = 0;
+    WaitClock clock;
     for (;;) {
         uint32_t done;
         asm volatile(
@@ -72,17 +72,14 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
             : "r"(addr), "r"(parity)
             : "memory");
         if (done) return true;
-        unsigned long long now;
-        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
-        if (start == 0) start = now;
-        else if (now - start > kWaitLimitNs) return false;
+        if (clock.ran_out(kWaitLimitNs)) return false;
     }
 }
 // The same without parking: for the one thread that issues the products, whose every wait stands
 // between the softmax warps and the tensor core.
 __device__ __forceinline__ bool mbar_wait_spin(uint64_t* bar, uint32_t parity) {
     const uint32_t addr = smem_addr(bar);
-    unsigned long long start = 0;
+    WaitClock clock;
     for (int spins = 0;; ++spins) {
         uint32_t done;
         asm volatile(
@@ -96,10 +93,7 @@ __device__ __forceinline__ bool mbar_wait_spin(uint64_t* bar, uint32_t parity) {
             : "memory");
         if (done) return true;
         if ((spins & 63) == 63) {
-            unsigned long long now;
-            asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
-            if (start == 0) start = now;
-            else if (now - start > kWaitLimitNs) return false;
+            if (clock.ran_out(kWaitLimitNs)) return false;
         }
     }
 }

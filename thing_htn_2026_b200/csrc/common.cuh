@@ -161,6 +161,27 @@ __device__ __forceinline__ float block_sum(float v, float* scratch /* >= 33 floa
     return scratch[32];
 }
 
+// The clock of the bounded waits on mbarriers: time by the global timer, in which a step from one
+// look at the timer to the next counts for kWaitStepCapNs at most.  Looks are microseconds apart
+// while a kernel runs; a longer step means that the GPU ran another process in between (time
+// slicing), and that time is not waiting: a wait that took it for such would give up with its
+// copies and products still in flight.
+constexpr unsigned long long kWaitStepCapNs = 100ull * 1000;
+struct WaitClock {
+    unsigned long long last = 0, waited = 0;
+    // One look at the timer.  True once the waiting seen so far exceeds limit_ns.
+    __device__ __forceinline__ bool ran_out(unsigned long long limit_ns) {
+        unsigned long long now;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+        if (last != 0) {
+            const unsigned long long step = now - last;
+            waited += step < kWaitStepCapNs ? step : kWaitStepCapNs;
+        }
+        last = now;
+        return waited > limit_ns;
+    }
+};
+
 // How attention scores are shaped between q . k and the softmax, beyond the plain scale:
 //   temperature  the scores of the query at position p are multiplied by
 //                1 + temp_coef * ln(floor((p + 1) / temp_every) + 1)       (temp_every 0: none)

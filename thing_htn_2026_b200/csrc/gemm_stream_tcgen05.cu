@@ -69,7 +69,7 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 // up to a microsecond per attempt, and the global timer ends the wait.  False: gave up.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
     const uint32_t addr = smem_addr(bar);
-    unsigned long long start = 0;
+    WaitClock clock;
     for (int spin = 0;; ++spin) {
         uint32_t done;
         asm volatile(
@@ -83,10 +83,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
             : "memory");
         if (done) return true;
         if ((spin & 7) == 7) {
-            unsigned long long now;
-            asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
-            if (start == 0) start = now;
-            else if (now - start > kWaitLimitNs) return false;
+            if (clock.ran_out(kWaitLimitNs)) return false;
         }
     }
 }
@@ -94,7 +91,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
 // products, whose every wait stands between HBM and the tensor core.
 __device__ __forceinline__ bool mbar_wait_spin(uint64_t* bar, uint32_t parity) {
     const uint32_t addr = smem_addr(bar);
-    unsigned long long start = 0;
+    WaitClock clock;
     for (int spin = 0;; ++spin) {
         uint32_t done;
         asm volatile(
@@ -108,10 +105,7 @@ __device__ __forceinline__ bool mbar_wait_spin(uint64_t* bar, uint32_t parity) {
             : "memory");
         if (done) return true;
         if ((spin & 63) == 63) {
-            unsigned long long now;
-            asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
-            if (start == 0) start = now;
-            else if (now - start > kWaitLimitNs) return false;
+            if (clock.ran_out(kWaitLimitNs)) return false;
         }
     }
 }

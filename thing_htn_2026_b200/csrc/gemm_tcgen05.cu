@@ -45,7 +45,7 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
 // Bounded wait for the phase with the given parity.  Returns false when it gave up.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
     const uint32_t addr = smem_addr(bar);
-    unsigned long long start = 0;
+    WaitClock clock;
     for (int spin = 0;; ++spin) {
         uint32_t done;
         asm volatile(
@@ -59,10 +59,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
             : "memory");
         if (done) return true;
         if ((spin & 63) == 63) {                  // look at the clock now and then
-            unsigned long long now;
-            asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
-            if (start == 0) start = now;
-            else if (now - start > kWaitLimitNs) return false;
+            if (clock.ran_out(kWaitLimitNs)) return false;
             __nanosleep(64);
         }
     }
