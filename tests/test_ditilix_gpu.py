@@ -363,6 +363,45 @@ def factor_at(p, coef, every):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("d, dv, n_q, n_kv, spare", [(16, 16, 2, 1, 0), (64, 64, 4, 2, 8), (48, 32, 3, 3, 0), (20, 36, 2, 1, 4),
+                                                    (128, 128, 2, 1, 0), (9, 5, 2, 2, 1), (24, 40, 1, 1, 3), (12, 12, 5, 1, 0)])
+def test_projected_rows_are_split_untouched(dtype, d, dv, n_q, n_kv, spare):
+    """Without norm and rotation `ops.qk_prepare` only splits a projected row: the queries come
+    back and the keys and values lie in the cache, bit for bit, at the positions of two sequences
+    of unequal lengths that cross a page border.  Sizes that allow 16-byte pieces and sizes that do
+    not (odd ones, rows with spare entries that break the alignment of the next row)."""
+    from thing_htn_2026_b200 import ops
+    from thing_htn_2026_b200.cache import KVSpec, SequenceCache
+    t = TORCH[dtype]
+    lens = [70, 3]
+    width = n_q * d + n_kv * (d + dv) + spare
+    g = torch.Generator().manual_seed(d * 100 + dv)
+    proj = torch.randn(sum(lens), width, generator=g).to(t)
+    cache = SequenceCache([KVSpec(n_kv, d, value_dim=dv)], max_tokens=64 * 4, dtype=t, device=DEV, max_slots=2)
+    slots = cache.open(2)
+    cache.prepare(slots, lens)
+    cu = torch.tensor([0, lens[0], sum(lens)], dtype=torch.int32, device=DEV)
+    rows = ops.step_rows(cu, torch.tensor(slots, dtype=torch.int32, device=DEV), cache.seq_lens, sum(lens), max(lens))
+    err = ops.new_error_word(DEV)
+    kv = cache.kv_view(0)
+    q = ops.qk_prepare(proj.to(DEV), None, None, None, 1.0, None, rows, kv, n_q, False, True, err)
+    assert int(err.item()) == 0
+    assert torch.equal(q.cpu(), proj[:, :n_q * d]), "queries"
+    storage = kv.storage.cpu().reshape(kv.storage.shape[0], -1)
+    page = kv.page_size
+    row = 0
+    for slot, n in zip(slots, lens):
+        pages = cache.book.pages_of(0, slot)
+        for pos in range(n):
+            flat = storage[pages[pos // page]]
+            keys = flat[:n_kv * page * d].reshape(n_kv, page, d)[:, pos % page]
+            values = flat[n_kv * page * d:].reshape(n_kv, page, dv)[:, pos % page]
+            assert torch.equal(keys.reshape(-1), proj[row, n_q * d:(n_q + n_kv) * d]), f"keys of position {pos}"
+            assert torch.equal(values.reshape(-1), proj[row, (n_q + n_kv) * d:(n_q + n_kv) * d + n_kv * dv]), f"values of position {pos}"
+            row += 1
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("d, dv, n_q, n_kv", [(16, 16, 2, 1), (64, 64, 4, 2), (48, 32, 3, 3), (20, 36, 2, 1), (128, 128, 2, 1)])
 @pytest.mark.parametrize("cap, coef, every", [(0.0, 0.0, 0), (0.0, -0.02, 1), (2.5, 0.0, 0), (4.0, 0.5, 16), (3.0, 1.0, 70)])
 def test_one_loud_key_among_hundreds_against_the_closed_form(dtype, d, dv, n_q, n_kv, cap, coef, every):

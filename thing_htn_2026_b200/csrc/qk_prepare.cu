@@ -250,12 +250,66 @@ __global__ void __launch_bounds__(128) qk_prepare_scalar_kernel(
     }
 }
 
+// No norm and no rotation: the projected row is only split, its queries to q_out, its keys and
+// values to the cache.  A copy in pieces of 16 bytes, for sizes and addresses that keep every
+// piece whole and aligned; the same bits as the kernels above produce.
+template <typename T>
+__global__ void __launch_bounds__(128) qk_split_kernel(
+    T* __restrict__ q_out, const T* __restrict__ proj, int proj_width, int values_are_keys,
+    const int* __restrict__ row_slot, const int* __restrict__ row_pos, PagedKV kv, int n_q, int write_cache,
+    int* __restrict__ err) {
+    pdl_launch_dependents();
+    pdl_wait();
+    constexpr int V = 16 / (int)sizeof(T);
+    const int m = blockIdx.x;
+    const int D = kv.head_dim, DV = kv.value_dim > 0 ? kv.value_dim : D;
+    const int nq = n_q * D, nk = kv.n_kv * D, nv = values_are_keys ? 0 : kv.n_kv * DV;
+    const T* src = proj + (size_t)m * proj_width;
+    const int pos = row_pos[m];
+    int page = -1;
+    if (write_cache) {
+        page = kv.block_table[(size_t)row_slot[m] * kv.bt_stride + pos / kv.page_size];
+        if (page < 0) {
+            if (threadIdx.x == 0 && err) atomicOr(err, THN_ERR_PAGE_UNMAPPED);
+            write_cache = 0;
+        }
+    }
+    const int in_page = pos % kv.page_size;
+    T* cache = (T*)kv.base;
+    const int pieces = (write_cache ? nq + nk + nv : nq) / V;
+    for (int piece = threadIdx.x; piece < pieces; piece += 128) {
+        const int e = piece * V;
+        const uint4 v = *reinterpret_cast<const uint4*>(src + e);
+        if (e < nq) {
+            *reinterpret_cast<uint4*>(q_out + (size_t)m * nq + e) = v;
+        } else if (e < nq + nk) {
+            const int kvh = (e - nq) / D, d = e - nq - kvh * D;
+            *reinterpret_cast<uint4*>(cache + kv_offset_sized(kv, page, 0, kvh, in_page) + d) = v;
+            if (values_are_keys) *reinterpret_cast<uint4*>(cache + kv_offset_sized(kv, page, 1, kvh, in_page) + d) = v;
+        } else {
+            const int kvh = (e - nq - nk) / DV, d = e - nq - nk - kvh * DV;
+            *reinterpret_cast<uint4*>(cache + kv_offset_sized(kv, page, 1, kvh, in_page) + d) = v;
+        }
+    }
+}
+
 template <typename T>
 int launch(void* q_out, const void* proj, int proj_width, const float* q_gain, const float* k_gain, int norm_scope,
            float gain_offset, float eps, const float* cos_tab, const float* sin_tab, int table_len, int rotary_dim,
            int interleaved, int values_are_keys, const int* row_slot, const int* row_pos, PagedKV kv, int n_rows,
            int n_q, int write_cache, int* err, cudaStream_t stream) {
     const int D = kv.head_dim, n_heads = n_q + kv.n_kv;
+    {
+        constexpr int V = 16 / (int)sizeof(T);
+        const int DV = kv.value_dim > 0 ? kv.value_dim : D;
+        const bool rotates = cos_tab != nullptr && rotary_dim > 0;
+        if (norm_scope == 0 && !rotates && D % V == 0 && DV % V == 0 && proj_width % V == 0 &&
+            (((uintptr_t)proj | (uintptr_t)q_out | (uintptr_t)kv.base) & 15) == 0) {
+            thn_launch(qk_split_kernel<T>, n_rows, 128, 0, stream, (T*)q_out, (const T*)proj, proj_width, values_are_keys,
+                       row_slot, row_pos, kv, n_q, write_cache, err);
+            return thn_launch_status("qk_prepare");
+        }
+    }
     const size_t smem = ((size_t)n_heads * D + n_heads) * sizeof(float);
     THN_UNSUPPORTED_IF(smem > 200 * 1024, "qk_prepare: %d heads of %d do not fit shared memory", n_heads, D);
     // pairs of adjacent entries need even sizes everywhere and pair-aligned addresses
