@@ -58,8 +58,11 @@ class StateSpec:
 
 
 # What one cache entry stores: keys and values, one state tensor, or several state tensors
-# (a tuple; ``state_view(entry, i)`` gives the i-th), or nothing.
-CacheNeed = Union[KVSpec, StateSpec, Tuple[StateSpec, ...], None]
+# (a tuple; ``state_view(entry, i)`` gives the i-th), or nothing.  A tuple may also hold ONE
+# KVSpec beside its state tensors (a mixer of two halves, one with keys and values, one with a
+# recurrent state): ``kv_view(entry)`` gives the keys and values, ``state_view(entry, i)`` the i-th
+# of the state tensors, counted without the KVSpec.
+CacheNeed = Union[KVSpec, StateSpec, Tuple[Union[KVSpec, StateSpec], ...], None]
 
 
 class SequenceCache:
@@ -86,8 +89,11 @@ class SequenceCache:
             if need is None:
                 continue
             places = []
-            for one in (need if isinstance(need, tuple) else (need,)):
-                if isinstance(one, KVSpec) and not isinstance(need, tuple):
+            ones = need if isinstance(need, tuple) else (need,)
+            if sum(isinstance(one, KVSpec) for one in ones) > 1:
+                raise TypeError(f"cache entry {entry}: more than one set of keys and values")
+            for one in ones:
+                if isinstance(one, KVSpec):
                     if one not in self.kv_specs:
                         self.kv_specs.append(one)
                     key = ("kv", self.kv_specs.index(one))
@@ -130,9 +136,10 @@ class SequenceCache:
         return self._named_state[name]
 
     def kv_view(self, entry: int) -> ops.KVView:
-        kind, g, i = self._entry_place[entry][0]
-        if kind != "kv":
+        held = [place for place in self._entry_place[entry] if place[0] == "kv"]
+        if not held:
             raise KeyError(f"cache entry {entry} holds state, not keys and values")
+        _, g, i = held[0]
         spec = self.kv_specs[g]
         return ops.KVView(self.kv_storage[g][i], self.block_tables[g], spec.n_kv, self.page_size, spec.head_dim,
                           spec.value_dim)
@@ -140,8 +147,8 @@ class SequenceCache:
     def state_view(self, entry: int, part: int = 0) -> torch.Tensor:
         """The entry's state tensor ``[max_slots, *shape]`` (the ``part``-th, where its need is a
         tuple of several)."""
-        places = self._entry_place[entry]
-        if places[0][0] != "state":
+        places = [place for place in self._entry_place[entry] if place[0] == "state"]
+        if not places:
             raise KeyError(f"cache entry {entry} holds keys and values, not state")
         if not 0 <= part < len(places):
             raise KeyError(f"cache entry {entry} holds {len(places)} state tensors, asked for number {part}")

@@ -63,6 +63,7 @@ def _decoder_model():
 
 def _register_builtin() -> None:
     from .bunudra import BunudraConfig
+    from .dubazen import DubazenConfig
     from .ditilix import DitilixConfig
     from .lanilix import LanilixConfig
     from .qwen3 import Qwen3Config
@@ -70,6 +71,7 @@ def _register_builtin() -> None:
     register_architecture(LanilixConfig.architecture, LanilixConfig, _decoder_model)
     register_architecture(BunudraConfig.architecture, BunudraConfig, _decoder_model)
     register_architecture(DitilixConfig.architecture, DitilixConfig, _decoder_model)
+    register_architecture(DubazenConfig.architecture, DubazenConfig, _decoder_model)
 
 
 _register_builtin()

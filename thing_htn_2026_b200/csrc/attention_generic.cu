@@ -16,6 +16,8 @@
 // (kv.value_dim); the output then has that size per head.  exact_weights keeps e in float32
 // where it multiplies V.  A ScoreShape (common.cuh) multiplies the scores of a row by a factor
 // that grows with the logarithm of its position and caps them with a tanh before the softmax.
+// With sinks (one float32 per query head) the softmax's denominator also holds exp(sink_h): a
+// term without key and value, unscaled, counted once; the running maximum starts from it.
 #include <math.h>
 
 #include "common.cuh"
@@ -27,7 +29,7 @@ __global__ void attention_generic_kernel(T* __restrict__ out, const T* __restric
                                          const int* __restrict__ row_slot, const int* __restrict__ row_pos,
                                          PagedKV kv, int n_rows, int n_q, float scale, int window,
                                          int keep_first, int chunk, int exact_weights, ScoreShape shape,
-                                         int* __restrict__ err) {
+                                         const float* __restrict__ sinks, int* __restrict__ err) {
     pdl_launch_dependents();
     pdl_wait();
     const int lane = threadIdx.x & 31;
@@ -48,6 +50,7 @@ __global__ void attention_generic_kernel(T* __restrict__ out, const T* __restric
         acc[i] = 0.f;
     }
     float run_max = -INFINITY, run_sum = 0.f;
+    if (sinks) { run_max = sinks[h]; run_sum = 1.0f; }     // the sink's own term, exp(sink - sink)
     int first = 0;
     if (window > 0 && pos - window + 1 > 0) first = pos - window + 1;
     if (chunk > 0) first = max(first, pos / chunk * chunk);
@@ -98,14 +101,14 @@ __global__ void attention_generic_kernel(T* __restrict__ out, const T* __restric
 template <typename T>
 static int launch_generic(void* out, const void* q, const int* row_slot, const int* row_pos, PagedKV kv, int n_rows,
                           int n_q, float scale, int window, int keep_first, int chunk, int exact_weights,
-                          ScoreShape shape, int* err, cudaStream_t stream) {
+                          ScoreShape shape, const float* sinks, int* err, cudaStream_t stream) {
     const int warps = 4;
     const long long units = (long long)n_rows * n_q;
     const unsigned blocks = (unsigned)((units + warps - 1) / warps);
     const int per_lane = (max(kv.head_dim, kv.value_dim) + 31) / 32;
 #define LAUNCH(N)                                                                                                  \
     thn_launch(attention_generic_kernel<T, N>, blocks, warps * 32, 0, stream, (T*)out, (const T*)q, row_slot, row_pos, kv, \
-                                                                      n_rows, n_q, scale, window, keep_first, chunk, exact_weights, shape, err)
+                                                                      n_rows, n_q, scale, window, keep_first, chunk, exact_weights, shape, sinks, err)
     if (per_lane <= 1) LAUNCH(1);
     else if (per_lane <= 2) LAUNCH(2);
     else if (per_lane <= 4) LAUNCH(4);
@@ -118,12 +121,13 @@ static int launch_generic(void* out, const void* q, const int* row_slot, const i
 // q [n_rows, n_q * head_dim], out [n_rows, n_q * value_dim]; the keys of a row are positions
 // [.., row_pos] of the sequence in row_slot, already in the cache.  window <= 0 means all keys
 // (keep_first is then without effect); chunk > 0: only the keys of the row's own chunk;
-// value_dim 0: values of the keys' size; softcap, temp_coef, temp_every: the ScoreShape (0: none).
+// value_dim 0: values of the keys' size; softcap, temp_coef, temp_every: the ScoreShape (0: none);
+// sinks float32 [n_q] or null.
 THN_API int thn_attention_generic(void* out, const void* q, const int* row_slot, const int* row_pos,
                                   const void* kv_base, const int* block_table, int bt_stride, int n_kv,
                                   int page_size, int head_dim, int value_dim, int n_rows, int n_q, float scale,
                                   int window, int keep_first, int chunk, int exact_weights, float softcap,
-                                  float temp_coef, int temp_every, int dtype, int* err, cudaStream_t stream) {
+                                  float temp_coef, int temp_every, const float* sinks, int dtype, int* err, cudaStream_t stream) {
     THN_CHECK_ARG(n_rows >= 0 && n_q > 0 && n_kv > 0 && page_size > 0, "attention_generic: bad sizes");
     THN_CHECK_ARG(n_q % n_kv == 0, "attention_generic: %d query heads are not a multiple of %d kv heads", n_q, n_kv);
     THN_UNSUPPORTED_IF(head_dim <= 0 || head_dim > 32 * kGenericMaxPerLane || value_dim < 0 ||
@@ -135,9 +139,9 @@ THN_API int thn_attention_generic(void* out, const void* q, const int* row_slot,
     if (n_rows == 0) return THN_OK;
     const ScoreShape shape{softcap, temp_coef, temp_every};
     PagedKV kv{kv_base, block_table, bt_stride, n_kv, page_size, head_dim, value_dim == head_dim ? 0 : value_dim};
-    if (dtype == THN_F32) return launch_generic<float>(out, q, row_slot, row_pos, kv, n_rows, n_q, scale, window, keep_first, chunk, exact_weights, shape, err, stream);
+    if (dtype == THN_F32) return launch_generic<float>(out, q, row_slot, row_pos, kv, n_rows, n_q, scale, window, keep_first, chunk, exact_weights, shape, sinks, err, stream);
     if (dtype == THN_BF16)
-        return launch_generic<__nv_bfloat16>(out, q, row_slot, row_pos, kv, n_rows, n_q, scale, window, keep_first, chunk, exact_weights, shape, err, stream);
+        return launch_generic<__nv_bfloat16>(out, q, row_slot, row_pos, kv, n_rows, n_q, scale, window, keep_first, chunk, exact_weights, shape, sinks, err, stream);
     THN_CHECK_ARG(false, "attention_generic: unknown dtype %d", dtype);
     return THN_OK;
 }

@@ -187,6 +187,91 @@ THN_API int thn_logistic_gate(void* out, const void* a, const void* g, long long
     return thn_launch_status("logistic_gate");
 }
 
+// out[m, c] = turn_back(a[m, head, :])[d] * logistic(g[m, c]) * scale, c = head * size + d: the
+// read-out of an attention whose values were turned by their positions before they were cached
+// (csrc/qk_prepare.cu) is turned back by the row's own position, pair i by -pos * f_i (the tables
+// hold cos and sin of +pos * f_i; layout 0: entry i pairs with i + rotary_dim / 2, 1: 2i with
+// 2i + 1), then gated.  Without tables it is the gate alone.  float32 inside, one rounding; the
+// output rows may be out_stride apart (a slice of a wider row).
+template <typename T>
+__global__ void rotate_gate_kernel(T* __restrict__ out, long long out_stride, const T* __restrict__ a,
+                                   const T* __restrict__ g, long long g_stride, const float* __restrict__ cos_tab,
+                                   const float* __restrict__ sin_tab, int table_len, int rotary_dim, int interleaved,
+                                   const int* __restrict__ row_pos, long long n, int n_heads, int size, float scale,
+                                   int* __restrict__ err) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= n) return;
+    const int width = n_heads * size;
+    const long long m = e / width;
+    const int c = (int)(e - m * width), d = c % size;
+    float v = to_f32<T>(a[e]);
+    if (cos_tab != nullptr && d < rotary_dim) {
+        const int pos = row_pos[m];
+        if (pos >= table_len) {
+            if (err) atomicOr(err, THN_ERR_POSITION_RANGE);
+            return;
+        }
+        const int half = rotary_dim / 2;
+        int i;
+        long long partner;
+        bool first;
+        if (interleaved) {
+            i = d >> 1; first = (d & 1) == 0; partner = first ? e + 1 : e - 1;
+        } else {
+            first = d < half; i = first ? d : d - half; partner = first ? e + half : e - half;
+        }
+        const float co = cos_tab[(size_t)pos * half + i], sn = sin_tab[(size_t)pos * half + i];
+        const float other = to_f32<T>(a[partner]);
+        v = first ? v * co + other * sn : v * co - other * sn;     // the turn by the negative angle
+    }
+    const float z = to_f32<T>(g[m * g_stride + c]);
+    out[m * out_stride + c] = from_f32<T>(v / (1.0f + expf(-z)) * scale);
+}
+
+THN_API int thn_rotate_gate(void* out, long long out_stride, const void* a, const void* g, long long g_stride,
+                            const float* cos_tab, const float* sin_tab, int table_len, int rotary_dim, int interleaved,
+                            const int* row_pos, int n_rows, int n_heads, int size, float scale, int dtype, int* err,
+                            cudaStream_t stream) {
+    THN_CHECK_ARG(n_rows >= 0 && n_heads > 0 && size > 0 && g_stride >= (long long)n_heads * size &&
+                      out_stride >= (long long)n_heads * size, "rotate_gate: bad sizes");
+    THN_CHECK_ARG(cos_tab == nullptr || (sin_tab != nullptr && row_pos != nullptr && rotary_dim % 2 == 0 &&
+                                         rotary_dim >= 0 && rotary_dim <= size),
+                  "rotate_gate: the rotation needs tables, positions and an even size within %d", size);
+    const long long n = (long long)n_rows * n_heads * size;
+    if (n == 0) return THN_OK;
+    const unsigned blocks = (unsigned)((n + 255) / 256);
+    if (dtype == THN_F32)
+        thn_launch(rotate_gate_kernel<float>, blocks, 256, 0, stream, (float*)out, out_stride, (const float*)a,
+                   (const float*)g, g_stride, cos_tab, sin_tab, table_len, rotary_dim, interleaved, row_pos, n, n_heads, size,
+                   scale, err);
+    else if (dtype == THN_BF16)
+        thn_launch(rotate_gate_kernel<__nv_bfloat16>, blocks, 256, 0, stream, (__nv_bfloat16*)out, out_stride,
+                   (const __nv_bfloat16*)a, (const __nv_bfloat16*)g, g_stride, cos_tab, sin_tab, table_len, rotary_dim,
+                   interleaved, row_pos, n, n_heads, size, scale, err);
+    else
+        THN_CHECK_ARG(false, "rotate_gate: unknown dtype %d", dtype);
+    return thn_launch_status("rotate_gate");
+}
+
+// x[m, c] += bias[c] * scale in place (float32): the bias of a product of the 32-bit path.
+__global__ void add_bias_f32_kernel(float* __restrict__ x, const float* __restrict__ bias, long long n, int width,
+                                    float scale) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (e < n) x[e] += bias[e % width] * scale;
+}
+
+THN_API int thn_add_bias_f32(float* x, const float* bias, int n_rows, int width, float scale, cudaStream_t stream) {
+    THN_CHECK_ARG(n_rows >= 0 && width > 0, "add_bias: bad sizes");
+    const long long n = (long long)n_rows * width;
+    if (n == 0) return THN_OK;
+    thn_launch(add_bias_f32_kernel, (unsigned)((n + 255) / 256), 256, 0, stream, x, bias, n, width, scale);
+    return thn_launch_status("add_bias");
+}
+
 // ------------------------------------------------------------------ RMSNorm
 
 constexpr int kNormThreads = 256;

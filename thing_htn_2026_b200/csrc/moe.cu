@@ -21,6 +21,8 @@
 //               A row holds [gates of all columns | ups of all columns]; the columns are
 //               [experts * ff | shared_ff].  The shared expert sees the token itself, has a limit
 //               of its own, and its columns are multiplied by logistic(gate logit of the row).
+//               With weight_output the routing weight multiplies the expert's activation instead
+//               (the expert sees the token itself and its output is weighted).
 #include <math.h>
 
 #include "common.cuh"
@@ -46,7 +48,8 @@ __device__ __forceinline__ Best warp_best(Best b) {
 
 __global__ void __launch_bounds__(kRouteWarps * 32) moe_route_kernel(
     float* __restrict__ dense, int* __restrict__ chosen, float* __restrict__ chosen_weight, const float* __restrict__ z,
-    long long z_stride, int n_rows, int n_experts, int n_groups, int keep, int top, float scale, int scoring) {
+    long long z_stride, int n_rows, int n_experts, int n_groups, int keep, int top, float scale, int scoring,
+    int renormalise, float renorm_eps) {
     pdl_launch_dependents();
     pdl_wait();
     extern __shared__ float shared[];     // per warp: scores [experts], group scores [groups]
@@ -146,6 +149,17 @@ __global__ void __launch_bounds__(kRouteWarps * 32) moe_route_kernel(
         }
         __syncwarp();
     }
+    if (renormalise && lane == 0) {
+        // the chosen experts' weights divided by their sum (+ renorm_eps), summed in the order chosen
+        float sum = 0.f;
+        for (int pick = 0; pick < top; ++pick) sum += chosen_weight[(size_t)row * top + pick];
+        const float r = scale / (sum / scale + renorm_eps);
+        for (int pick = 0; pick < top; ++pick) {
+            const float w = chosen_weight[(size_t)row * top + pick] / scale * r;
+            chosen_weight[(size_t)row * top + pick] = w;
+            dense[(size_t)row * n_experts + chosen[(size_t)row * top + pick]] = w;
+        }
+    }
 }
 
 __device__ __forceinline__ float gelu_exact(float u) { return 0.5f * u * (1.0f + erff(u * 0.70710678118654752f)); }
@@ -205,7 +219,8 @@ __global__ void routed_gelu_bf16_vec_kernel(__nv_bfloat16* __restrict__ out, con
 template <typename T>
 __global__ void routed_clamped_glu_kernel(T* __restrict__ out, const T* __restrict__ gu, const float* __restrict__ dense,
                                           const float* __restrict__ shared_logit, long long logit_stride, long long n,
-                                          int width, int n_experts, int ff, float limit, float shared_limit, float alpha) {
+                                          int width, int n_experts, int ff, float limit, float shared_limit, float alpha,
+                                          int weight_output) {
     pdl_launch_dependents();
     pdl_wait();
     const long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -217,6 +232,7 @@ __global__ void routed_clamped_glu_kernel(T* __restrict__ out, const T* __restri
         w = dense[row * n_experts + c / ff];
         lim = limit;
         if (w == 0.f) { out[e] = from_f32<T>(0.f); return; }
+        if (weight_output) { after = w; w = 1.0f; }
     } else if (shared_logit) {
         after = 1.0f / (1.0f + expf(-shared_logit[row * logit_stride]));
     }
@@ -231,7 +247,7 @@ __global__ void routed_clamped_glu_kernel(T* __restrict__ out, const T* __restri
 __global__ void routed_clamped_glu_bf16_vec_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ gu,
                                                    const float* __restrict__ dense, const float* __restrict__ shared_logit,
                                                    long long logit_stride, int width, int n_experts, int ff, float limit,
-                                                   float shared_limit, float alpha) {
+                                                   float shared_limit, float alpha, int weight_output) {
     pdl_launch_dependents();
     pdl_wait();
     const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
@@ -246,6 +262,7 @@ __global__ void routed_clamped_glu_bf16_vec_kernel(__nv_bfloat16* __restrict__ o
     }
     uint4 packed = make_uint4(0, 0, 0, 0);
     if (w != 0.f) {
+        if (weight_output && c < n_experts * ff) { after = w; w = 1.0f; }
         const uint4 gv = *reinterpret_cast<const uint4*>(gu + row * 2 * width + c);
         const uint4 uv = *reinterpret_cast<const uint4*>(gu + row * 2 * width + width + c);
         const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&gv);
@@ -268,10 +285,12 @@ __global__ void routed_clamped_glu_bf16_vec_kernel(__nv_bfloat16* __restrict__ o
 // z float32 [rows, >= experts] with rows z_stride apart; dense float32 [rows, experts]; chosen
 // int32 and chosen_weight float32 [rows, top].
 THN_API int thn_moe_route(float* dense, int* chosen, float* chosen_weight, const float* z, long long z_stride, int n_rows,
-                          int n_experts, int n_groups, int keep, int top, float scale, int scoring, cudaStream_t stream) {
+                          int n_experts, int n_groups, int keep, int top, float scale, int scoring, int renormalise,
+                          float renorm_eps, cudaStream_t stream) {
     THN_CHECK_ARG(n_rows >= 0 && n_experts > 0 && n_groups > 0 && n_experts % n_groups == 0,
                   "moe_route: %d experts in %d groups", n_experts, n_groups);
     THN_CHECK_ARG(scoring == 0 || scoring == 1, "moe_route: scoring %d (0: softmax, 1: logistic)", scoring);
+    THN_CHECK_ARG(!renormalise || (scoring == 0 && scale != 0.f), "moe_route: weights are renormalised with softmax scores only");
     THN_CHECK_ARG(keep > 0 && keep <= n_groups && top > 0 && top <= keep * (n_experts / n_groups),
                   "moe_route: top %d of the experts of %d groups out of %d", top, keep, n_groups);
     THN_UNSUPPORTED_IF(n_experts > 4096, "moe_route: %d experts, at most 4096", n_experts);
@@ -280,7 +299,7 @@ THN_API int thn_moe_route(float* dense, int* chosen, float* chosen_weight, const
     if (smem > 32 * 1024)
         cudaFuncSetAttribute(moe_route_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     thn_launch(moe_route_kernel, (n_rows + kRouteWarps - 1) / kRouteWarps, kRouteWarps * 32, smem, stream, dense, chosen,
-               chosen_weight, z, z_stride, n_rows, n_experts, n_groups, keep, top, scale, scoring);
+               chosen_weight, z, z_stride, n_rows, n_experts, n_groups, keep, top, scale, scoring, renormalise, renorm_eps);
     return thn_launch_status("moe_route");
 }
 
@@ -316,7 +335,7 @@ THN_API int thn_routed_gelu(void* out, const void* u, const float* dense, const 
 // rows' gate logits of the shared expert, logit_stride apart (null: no gate).
 THN_API int thn_routed_clamped_glu(void* out, const void* gu, const float* dense, const float* shared_logit,
                                    long long logit_stride, int n_rows, int n_experts, int ff, int shared_ff, float limit,
-                                   float shared_limit, float alpha, int dtype, cudaStream_t stream) {
+                                   float shared_limit, float alpha, int weight_output, int dtype, cudaStream_t stream) {
     THN_CHECK_ARG(n_rows >= 0 && n_experts >= 0 && ff >= 0 && shared_ff >= 0 && n_experts * ff + shared_ff > 0,
                   "routed_clamped_glu: bad sizes");
     THN_CHECK_ARG((n_experts * ff == 0 || limit > 0.f) && (shared_ff == 0 || shared_limit > 0.f),
@@ -329,16 +348,16 @@ THN_API int thn_routed_clamped_glu(void* out, const void* gu, const float* dense
         ((((uintptr_t)out) | ((uintptr_t)gu)) & 15) == 0) {
         thn_launch(routed_clamped_glu_bf16_vec_kernel, dim3((width / 8 + 127) / 128, n_rows), 128, 0, stream,
                    (__nv_bfloat16*)out, (const __nv_bfloat16*)gu, dense, shared_logit, logit_stride, width, n_experts, ff,
-                   limit, shared_limit, alpha);
+                   limit, shared_limit, alpha, weight_output);
         return thn_launch_status("routed_clamped_glu");
     }
     if (dtype == THN_F32)
         thn_launch(routed_clamped_glu_kernel<float>, blocks, 256, 0, stream, (float*)out, (const float*)gu, dense,
-                   shared_logit, logit_stride, n, width, n_experts, ff, limit, shared_limit, alpha);
+                   shared_logit, logit_stride, n, width, n_experts, ff, limit, shared_limit, alpha, weight_output);
     else if (dtype == THN_BF16)
         thn_launch(routed_clamped_glu_kernel<__nv_bfloat16>, blocks, 256, 0, stream, (__nv_bfloat16*)out,
                    (const __nv_bfloat16*)gu, dense, shared_logit, logit_stride, n, width, n_experts, ff, limit, shared_limit,
-                   alpha);
+                   alpha, weight_output);
     else
         THN_CHECK_ARG(false, "routed_clamped_glu: unknown dtype %d", dtype);
     return thn_launch_status("routed_clamped_glu");

@@ -267,7 +267,8 @@ int launch(void* y, float* h, const void* d, const void* d2, float mult, NormArg
 template <typename T>
 __global__ void gated_head_norm_kernel(T* __restrict__ out, const float* __restrict__ o, const T* __restrict__ gate,
                                        long long gate_stride, const float* __restrict__ w, float eps, long long n_units,
-                                       int n_heads, int size, int w_stride, int gate_kind) {
+                                       int n_heads, int size, int w_stride, int gate_kind, long long out_stride,
+                                       float scale) {
     pdl_launch_dependents();
     pdl_wait();
     const int lane = threadIdx.x & 31;
@@ -285,7 +286,8 @@ __global__ void gated_head_norm_kernel(T* __restrict__ out, const float* __restr
     for (int i = lane; i < size; i += 32) {
         const float z = to_f32<T>(g[i]);
         const float logistic = 1.0f / (1.0f + expf(-z));
-        out[unit * size + i] = from_f32<T>(src[i] * rstd * wh[i] * (gate_kind ? logistic : z * logistic));
+        out[m * out_stride + (long long)head * size + i] =
+            from_f32<T>(src[i] * rstd * wh[i] * (gate_kind ? logistic : z * logistic) * scale);
     }
 }
 // The same with four consecutive entries per lane (16-byte loads of the read-out, 8-byte loads
@@ -360,17 +362,21 @@ THN_API int thn_residual_norm(void* y, float* h, const void* d, const void* d2, 
 
 // o float32 [rows, n_heads, size]; gate of the activation type, row stride gate_stride
 // elements; w float32 [size] (w_per_head 0) or [n_heads * size] (w_per_head 1); gate_kind 0: silu,
-// 1: logistic; out of the activation type [rows, n_heads * size].
+// 1: logistic; out of the activation type [rows, n_heads * size], its rows out_stride elements apart
+// (0: n_heads * size); scale: a constant factor on the result.
 THN_API int thn_gated_head_norm(void* out, const float* o, const void* gate, long long gate_stride, const float* w,
-                                float eps, int rows, int n_heads, int size, int w_per_head, int gate_kind, int dtype,
-                                cudaStream_t stream) {
+                                float eps, int rows, int n_heads, int size, int w_per_head, int gate_kind,
+                                long long out_stride, float scale, int dtype, cudaStream_t stream) {
     THN_CHECK_ARG(rows >= 0 && n_heads > 0 && size > 0 && eps > 0.f, "gated_head_norm: bad sizes");
     const long long units = (long long)rows * n_heads;
     if (units == 0) return THN_OK;
     const int warps = 4;
     const unsigned blocks = (unsigned)((units + warps - 1) / warps);
     const int w_stride = w_per_head ? size : 0;
-    if (dtype == THN_BF16 && !w_per_head && gate_kind == 0 && size % 4 == 0 && gate_stride % 4 == 0 &&
+    if (out_stride <= 0) out_stride = (long long)n_heads * size;
+    THN_CHECK_ARG(out_stride >= (long long)n_heads * size, "gated_head_norm: output rows %lld apart are too short", out_stride);
+    if (dtype == THN_BF16 && !w_per_head && gate_kind == 0 && size % 4 == 0 && gate_stride % 4 == 0 && scale == 1.0f &&
+        out_stride == (long long)n_heads * size &&
         ((((uintptr_t)o | (uintptr_t)w) & 15) | (((uintptr_t)gate | (uintptr_t)out) & 7)) == 0) {
         thn_launch(gated_head_norm_bf16_vec_kernel, blocks, warps * 32, 0, stream, (__nv_bfloat16*)out, o,
                    (const __nv_bfloat16*)gate, gate_stride, w, eps, units, n_heads, size);
@@ -378,10 +384,11 @@ THN_API int thn_gated_head_norm(void* out, const float* o, const void* gate, lon
     }
     if (dtype == THN_F32)
         thn_launch(gated_head_norm_kernel<float>, blocks, warps * 32, 0, stream, (float*)out, o, (const float*)gate,
-                   gate_stride, w, eps, units, n_heads, size, w_stride, gate_kind);
+                   gate_stride, w, eps, units, n_heads, size, w_stride, gate_kind, out_stride, scale);
     else if (dtype == THN_BF16)
         thn_launch(gated_head_norm_kernel<__nv_bfloat16>, blocks, warps * 32, 0, stream, (__nv_bfloat16*)out, o,
-                   (const __nv_bfloat16*)gate, gate_stride, w, eps, units, n_heads, size, w_stride, gate_kind);
+                   (const __nv_bfloat16*)gate, gate_stride, w, eps, units, n_heads, size, w_stride, gate_kind, out_stride,
+                   scale);
     else
         THN_CHECK_ARG(false, "gated_head_norm: unknown dtype %d", dtype);
     return thn_launch_status("gated_head_norm");

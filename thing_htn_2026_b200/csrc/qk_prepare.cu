@@ -12,6 +12,9 @@
 //   values       0: the row brings values of its own, [q | k | v] (a value may have a size of its
 //                   own, value_dim);
 //                1: the values are the keys as projected, before norm and rotation, [q | k].
+//   value rotation   with tables of their own (v_rotary_dim entries of every value, in the layout of
+//                the keys' rotation) the values of the row are turned by its position before they
+//                go to the cache; a reader turns its output back by its own position.
 #include "common.cuh"
 
 namespace {
@@ -60,7 +63,8 @@ __global__ void __launch_bounds__(THREADS) qk_prepare_kernel(
     const float* __restrict__ k_gain, int norm_scope, float gain_offset, float eps, const float* __restrict__ cos_tab,
     const float* __restrict__ sin_tab, int table_len, int rotary_dim, int interleaved, int values_are_keys,
     const int* __restrict__ row_slot, const int* __restrict__ row_pos, PagedKV kv, int n_q, int write_cache,
-    int half_d_shift, int* __restrict__ err) {
+    int half_d_shift, const float* __restrict__ v_cos, const float* __restrict__ v_sin, int v_table_len, int v_rotary_dim,
+    int* __restrict__ err) {
     pdl_launch_dependents();
     pdl_wait();
     extern __shared__ __align__(8) float vals[];   // [(n_q + n_kv) * D] raw values; then [n_q + n_kv] scales per head
@@ -96,10 +100,31 @@ __global__ void __launch_bounds__(THREADS) qk_prepare_kernel(
     }
     if (write_cache && !values_are_keys) {
         const int DV = kv.value_dim > 0 ? kv.value_dim : D;
-        for (int pair = threadIdx.x; pair < kv.n_kv * DV / 2; pair += THREADS) {
-            const int e = 2 * pair, kvh = e / DV, d = e - kvh * DV;
-            const float2 v = Pair<T>::load(src + total + e);
-            Pair<T>::store((T*)kv.base + kv_offset_sized(kv, page, 1, kvh, in_page) + d, v.x, v.y);
+        const bool turn = v_cos != nullptr && v_rotary_dim > 0;
+        if (turn && pos >= v_table_len) {
+            if (threadIdx.x == 0 && err) atomicOr(err, THN_ERR_POSITION_RANGE);
+        } else {
+            const int v_half = v_rotary_dim / 2;
+            for (int pair = threadIdx.x; pair < kv.n_kv * DV / 2; pair += THREADS) {
+                const int e = 2 * pair, kvh = e / DV, d = e - kvh * DV;
+                float2 v = Pair<T>::load(src + total + e);
+                if (turn && d < v_rotary_dim) {
+                    const float* c_row = v_cos + (size_t)pos * v_half;
+                    const float* s_row = v_sin + (size_t)pos * v_half;
+                    if (interleaved) {
+                        const float c = c_row[d >> 1], sn = s_row[d >> 1];
+                        v = make_float2(v.x * c - v.y * sn, v.y * c + v.x * sn);
+                    } else {
+                        // d and d + 1 lie in the same half (the launcher sends an odd half to the scalar kernel)
+                        const bool first = d < v_half;
+                        const int i = first ? d : d - v_half;
+                        const float2 o = Pair<T>::load(src + total + (first ? e + v_half : e - v_half));
+                        v = first ? make_float2(v.x * c_row[i] - o.x * s_row[i], v.y * c_row[i + 1] - o.y * s_row[i + 1])
+                                  : make_float2(v.x * c_row[i] + o.x * s_row[i], v.y * c_row[i + 1] + o.y * s_row[i + 1]);
+                    }
+                }
+                Pair<T>::store((T*)kv.base + kv_offset_sized(kv, page, 1, kvh, in_page) + d, v.x, v.y);
+            }
         }
     }
     float rq = 1.f, rk = 1.f;
@@ -168,6 +193,7 @@ __global__ void __launch_bounds__(128) qk_prepare_scalar_kernel(
     const float* __restrict__ k_gain, int norm_scope, float gain_offset, float eps, const float* __restrict__ cos_tab,
     const float* __restrict__ sin_tab, int table_len, int rotary_dim, int interleaved, int values_are_keys,
     const int* __restrict__ row_slot, const int* __restrict__ row_pos, PagedKV kv, int n_q, int write_cache,
+    const float* __restrict__ v_cos, const float* __restrict__ v_sin, int v_table_len, int v_rotary_dim,
     int* __restrict__ err) {
     pdl_launch_dependents();
     pdl_wait();
@@ -196,9 +222,27 @@ __global__ void __launch_bounds__(128) qk_prepare_scalar_kernel(
     const int in_page = pos % kv.page_size;
     if (write_cache) {
         const int DV = !values_are_keys && kv.value_dim > 0 ? kv.value_dim : D;
+        const bool turn = !values_are_keys && v_cos != nullptr && v_rotary_dim > 0;
+        if (turn && pos >= v_table_len) {
+            if (threadIdx.x == 0 && err) atomicOr(err, THN_ERR_POSITION_RANGE);
+            return;
+        }
+        const int v_half = v_rotary_dim / 2;
         for (int e = threadIdx.x; e < kv.n_kv * DV; e += blockDim.x) {
             const int kvh = e / DV, d = e - kvh * DV;
-            const T v = values_are_keys ? src[nq + e] : src[total + e];
+            T v = values_are_keys ? src[nq + e] : src[total + e];
+            if (turn && d < v_rotary_dim) {
+                int i, partner;
+                bool first;
+                if (interleaved) {
+                    i = d >> 1; first = (d & 1) == 0; partner = first ? e + 1 : e - 1;
+                } else {
+                    first = d < v_half; i = first ? d : d - v_half; partner = first ? e + v_half : e - v_half;
+                }
+                const float c = v_cos[(size_t)pos * v_half + i], sn = v_sin[(size_t)pos * v_half + i];
+                const float own = to_f32<T>(v), other = to_f32<T>(src[total + partner]);
+                v = from_f32<T>(first ? own * c - other * sn : own * c + other * sn);
+            }
             ((T*)kv.base)[kv_offset_sized(kv, page, 1, kvh, in_page) + d] = v;
         }
     }
@@ -297,13 +341,14 @@ template <typename T>
 int launch(void* q_out, const void* proj, int proj_width, const float* q_gain, const float* k_gain, int norm_scope,
            float gain_offset, float eps, const float* cos_tab, const float* sin_tab, int table_len, int rotary_dim,
            int interleaved, int values_are_keys, const int* row_slot, const int* row_pos, PagedKV kv, int n_rows,
-           int n_q, int write_cache, int* err, cudaStream_t stream) {
+           int n_q, int write_cache, const float* v_cos, const float* v_sin, int v_table_len, int v_rotary_dim, int* err,
+           cudaStream_t stream) {
     const int D = kv.head_dim, n_heads = n_q + kv.n_kv;
     {
         constexpr int V = 16 / (int)sizeof(T);
         const int DV = kv.value_dim > 0 ? kv.value_dim : D;
         const bool rotates = cos_tab != nullptr && rotary_dim > 0;
-        if (norm_scope == 0 && !rotates && D % V == 0 && DV % V == 0 && proj_width % V == 0 &&
+        if (norm_scope == 0 && !rotates && !(v_cos != nullptr && v_rotary_dim > 0) && D % V == 0 && DV % V == 0 && proj_width % V == 0 &&
             (((uintptr_t)proj | (uintptr_t)q_out | (uintptr_t)kv.base) & 15) == 0) {
             thn_launch(qk_split_kernel<T>, n_rows, 128, 0, stream, (T*)q_out, (const T*)proj, proj_width, values_are_keys,
                        row_slot, row_pos, kv, n_q, write_cache, err);
@@ -314,13 +359,14 @@ int launch(void* q_out, const void* proj, int proj_width, const float* q_gain, c
     THN_UNSUPPORTED_IF(smem > 200 * 1024, "qk_prepare: %d heads of %d do not fit shared memory", n_heads, D);
     // pairs of adjacent entries need even sizes everywhere and pair-aligned addresses
     const bool pairs = D % 2 == 0 && kv.value_dim % 2 == 0 && proj_width % 2 == 0 && (interleaved || (rotary_dim / 2) % 2 == 0) &&
+                       (interleaved || v_cos == nullptr || (v_rotary_dim / 2) % 2 == 0) &&
                        (((uintptr_t)proj | (uintptr_t)q_out | (uintptr_t)kv.base) & (2 * sizeof(T) - 1)) == 0;
     if (!pairs) {
         if (smem > 32 * 1024)
             cudaFuncSetAttribute(qk_prepare_scalar_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         thn_launch(qk_prepare_scalar_kernel<T>, n_rows, 128, smem, stream, (T*)q_out, (const T*)proj, proj_width, q_gain,
                    k_gain, norm_scope, gain_offset, eps, cos_tab, sin_tab, table_len, rotary_dim, interleaved,
-                   values_are_keys, row_slot, row_pos, kv, n_q, write_cache, err);
+                   values_are_keys, row_slot, row_pos, kv, n_q, write_cache, v_cos, v_sin, v_table_len, v_rotary_dim, err);
         return thn_launch_status("qk_prepare");
     }
     int shift = -1;
@@ -333,7 +379,8 @@ int launch(void* q_out, const void* proj, int proj_width, const float* q_gain, c
             cudaFuncSetAttribute(qk_prepare_kernel<T, THREADS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
         thn_launch(qk_prepare_kernel<T, THREADS>, n_rows, THREADS, smem, stream, (T*)q_out, (const T*)proj, proj_width, \
                    q_gain, k_gain, norm_scope, gain_offset, eps, cos_tab, sin_tab, table_len, rotary_dim, interleaved, \
-                   values_are_keys, row_slot, row_pos, kv, n_q, write_cache, shift, err);                             \
+                   values_are_keys, row_slot, row_pos, kv, n_q, write_cache, shift, v_cos, v_sin, v_table_len,         \
+                   v_rotary_dim, err);                                                                                \
     } while (0)
     if (n_rows <= 64 && n_heads * D >= 2048) THN_QK_LAUNCH(512);
     else if (n_heads * D >= 4096) THN_QK_LAUNCH(256);
@@ -347,7 +394,8 @@ THN_API int thn_qk_prepare(void* q_out, const void* proj, int proj_width, const 
                            int norm_scope, float gain_offset, float eps, const float* cos_tab, const float* sin_tab,
                            int table_len, int rotary_dim, int interleaved, int values_are_keys, const int* row_slot,
                            const int* row_pos, void* kv_base, const int* block_table, int bt_stride, int n_kv,
-                           int page_size, int head_dim, int value_dim, int n_rows, int n_q, int write_cache, int dtype,
+                           int page_size, int head_dim, int value_dim, int n_rows, int n_q, int write_cache,
+                           const float* v_cos, const float* v_sin, int v_table_len, int v_rotary_dim, int dtype,
                            int* err, cudaStream_t stream) {
     THN_CHECK_ARG(n_rows >= 0 && n_q > 0 && n_kv > 0 && head_dim > 0 && page_size > 0, "qk_prepare: bad sizes");
     THN_CHECK_ARG(norm_scope >= 0 && norm_scope <= 2, "qk_prepare: norm scope %d", norm_scope);
@@ -355,6 +403,9 @@ THN_API int thn_qk_prepare(void* q_out, const void* proj, int proj_width, const 
     THN_CHECK_ARG(rotary_dim >= 0 && rotary_dim <= head_dim && rotary_dim % 2 == 0,
                   "qk_prepare: rotary_dim %d must be even and within the head size %d", rotary_dim, head_dim);
     if (value_dim <= 0) value_dim = head_dim;
+    THN_CHECK_ARG(v_cos == nullptr || (v_sin != nullptr && !values_are_keys && v_rotary_dim >= 0 && v_rotary_dim % 2 == 0 &&
+                                       v_rotary_dim <= value_dim),
+                  "qk_prepare: a rotation of the values needs values of their own and an even size within %d", value_dim);
     THN_CHECK_ARG(!values_are_keys || value_dim == head_dim, "qk_prepare: values that are the keys have the keys' size");
     THN_CHECK_ARG(proj_width >= (n_q + n_kv) * head_dim + (values_are_keys ? 0 : n_kv * value_dim),
                   "qk_prepare: rows of %d are too short", proj_width);
@@ -363,11 +414,11 @@ THN_API int thn_qk_prepare(void* q_out, const void* proj, int proj_width, const 
     if (dtype == THN_F32)
         return launch<float>(q_out, proj, proj_width, q_gain, k_gain, norm_scope, gain_offset, eps, cos_tab, sin_tab,
                              table_len, rotary_dim, interleaved, values_are_keys, row_slot, row_pos, kv, n_rows, n_q,
-                             write_cache, err, stream);
+                             write_cache, v_cos, v_sin, v_table_len, v_rotary_dim, err, stream);
     if (dtype == THN_BF16)
         return launch<__nv_bfloat16>(q_out, proj, proj_width, q_gain, k_gain, norm_scope, gain_offset, eps, cos_tab,
                                      sin_tab, table_len, rotary_dim, interleaved, values_are_keys, row_slot, row_pos, kv,
-                                     n_rows, n_q, write_cache, err, stream);
+                                     n_rows, n_q, write_cache, v_cos, v_sin, v_table_len, v_rotary_dim, err, stream);
     THN_CHECK_ARG(false, "qk_prepare: unknown dtype %d", dtype);
     return THN_OK;
 }

@@ -98,6 +98,12 @@ class DecoderModel:
         """Final norm and head at the given rows (int32 indices; None: every row): float32.
         ``err``: the step's device error word."""
         post = None
+        if isinstance(d, Branch) and d.write is not None:
+            # several copies of the stream: the last sublayer's write, then the norm of the copies' sum
+            y = d.tensor
+            if rows is not None:
+                h, y = ops.gather_rows(h, rows), ops.gather_rows(y, rows)
+            return self.head.forward(self.final_norm.stream_norm(h, d.write.write.numel(), y=y, written=d.write)[1], err)
         if isinstance(d, Branch) and (d.second is not None or d.factor != 1.0):
             # two sublayers side by side, or a factor on the add: the norm takes the branch whole
             post = d.norm

@@ -56,17 +56,30 @@ _SIGNATURES = {
                                         c_void_p, c_void_p],
     "thn_attention_generic": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                               c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_int, c_float, c_float, c_int,
-                              c_int, c_void_p, c_void_p],
+                              c_void_p, c_int, c_void_p, c_void_p],
     "thn_residual_norm": [c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_float, c_float, c_int,
                           c_void_p, c_void_p, c_float, c_float, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "thn_gated_head_norm": [c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_float, c_int, c_int, c_int, c_int,
-                            c_int, c_int, c_void_p],
+                            c_int, c_longlong, c_float, c_int, c_void_p],
+    "thn_hyper_norm": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float,
+                       c_int, c_int, c_int, c_int, c_void_p],
+    "thn_linear_attention": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p,
+                             c_float, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_void_p],
+    "thn_causal_conv": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                        c_int, c_int, c_int, c_int, c_void_p],
+    "thn_conv_ring_update": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                             c_void_p],
+    "thn_selective_scan": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+                           c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "thn_rotate_gate": [c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_int, c_int,
+                        c_void_p, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p],
+    "thn_add_bias_f32": [c_void_p, c_void_p, c_int, c_int, c_float, c_void_p],
     "thn_gather_rows_scaled": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_int,
                                c_void_p, c_void_p],
     "thn_scale_f32": [c_void_p, c_longlong, c_float, c_void_p],
     "thn_polynorm": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p],
     "thn_routed_clamped_glu": [c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_float,
-                               c_float, c_float, c_int, c_void_p],
+                               c_float, c_float, c_int, c_int, c_void_p],
     "thn_logistic_gate": [c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_void_p],
     "thn_latent_norm": [c_void_p, c_void_p, c_longlong, c_void_p, c_float, c_int, c_int, c_int, c_void_p],
     "thn_latent_assemble": [c_void_p, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int,
@@ -77,12 +90,12 @@ _SIGNATURES = {
     "thn_mlstm_recurrence": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_float, c_int,
                              c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_void_p],
     "thn_moe_route": [c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int, c_float,
-                      c_int, c_void_p],
+                      c_int, c_int, c_float, c_void_p],
     "thn_routed_gelu": [c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "thn_clamped_glu": [c_void_p, c_void_p, c_int, c_int, c_float, c_float, c_int, c_void_p],
     "thn_qk_prepare": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_float, c_float, c_void_p, c_void_p,
                        c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
-                       c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+                       c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p],
     "thn_delta_prepare": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                           c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                           c_float, c_int, c_void_p],
@@ -478,11 +491,14 @@ GATE_KINDS = {"silu": 0, "logistic": 1}
 
 
 def gated_head_norm(o: torch.Tensor, gate: torch.Tensor, gate_offset: int, weight: torch.Tensor, eps: float,
-                    n_heads: int, size: int, dtype: torch.dtype, gate_kind: str = "silu") -> torch.Tensor:
+                    n_heads: int, size: int, dtype: torch.dtype, gate_kind: str = "silu", scale: float = 1.0,
+                    out: Optional[torch.Tensor] = None, out_offset: int = 0) -> torch.Tensor:
     """o float32 [rows, heads, size] -> o / sqrt(mean over size + eps) * weight * act(gate), of
     ``dtype`` [rows, heads * size]; the gate of a row is ``gate[row, gate_offset : gate_offset +
     heads * size]``; ``weight`` has ``size`` entries (shared by the heads) or ``heads * size``;
-    ``gate_kind`` "silu" or "logistic"."""
+    ``gate_kind`` "silu" or "logistic"; ``scale``: a constant factor on the result.  One head of
+    ``heads * size`` entries is a norm over all heads together.  With ``out`` (rows of ``dtype``, at
+    least ``out_offset + heads * size`` wide) the result goes to its columns from ``out_offset``."""
     _need(o, "gated_head_norm o", torch.float32)
     _need(gate, "gated_head_norm gate", dtype)
     _need(weight, "gated_head_norm weight", torch.float32)
@@ -490,10 +506,16 @@ def gated_head_norm(o: torch.Tensor, gate: torch.Tensor, gate_offset: int, weigh
     if o.numel() != rows * n_heads * size or weight.shape[0] not in (size, n_heads * size) or gate.shape[0] != rows \
             or gate_offset + n_heads * size > gate.shape[1]:
         raise KernelError(f"gated_head_norm: shapes o {tuple(o.shape)}, gate {tuple(gate.shape)}, weight {tuple(weight.shape)}")
-    out = torch.empty((rows, n_heads * size), dtype=dtype, device=o.device)
+    if out is None:
+        out, out_offset = torch.empty((rows, n_heads * size), dtype=dtype, device=o.device), 0
+    else:
+        _need(out, "gated_head_norm out", dtype)
+        if out.shape[0] != rows or out_offset < 0 or out_offset + n_heads * size > out.shape[1]:
+            raise KernelError(f"gated_head_norm: out {tuple(out.shape)} has no room for {n_heads * size} columns from {out_offset}")
     gate_ptr = gate.data_ptr() + gate_offset * gate.element_size()
-    _call("thn_gated_head_norm", _ptr(out), _ptr(o), gate_ptr, gate.shape[1], _ptr(weight), float(eps), rows, n_heads,
-          size, int(weight.shape[0] != size), GATE_KINDS[gate_kind], DTYPE_CODE[dtype], _stream())
+    _call("thn_gated_head_norm", out.data_ptr() + out_offset * out.element_size(), _ptr(o), gate_ptr, gate.shape[1],
+          _ptr(weight), float(eps), rows, n_heads, size, int(weight.shape[0] != size and n_heads > 1), GATE_KINDS[gate_kind],
+          out.shape[1], float(scale), DTYPE_CODE[dtype], _stream())
     return out
 
 
@@ -621,14 +643,31 @@ def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, err: Optional[torch.
 
 
 def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
-           err: Optional[torch.Tensor] = None) -> torch.Tensor:
+           err: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
     """x [M, K] @ weight[N, K]^T.  float32: this library's FFMA kernel.  bfloat16 with few
     rows and a deep reduction or a tall weight: this library's weight-streaming kernel
     (``err``: the step's device error word for its bounded waits).  bfloat16 with a float32 result
     of at most 64 columns (a router, a gate): this library's warp-per-row kernel.  bfloat16 otherwise: the
     vendor library's tensor-core product with float32 accumulation (the reference's choice,
     engine/engine.py:341-350).  ``out_dtype=torch.float32`` keeps the accumulator's
-    precision (used for logits)."""
+    precision (used for logits).  ``bias`` (of the activation type, ``[N]``) is added to every row:
+    in the vendor product's epilogue (float32, before the one rounding), or by a kernel of its own
+    after the FFMA product."""
+    if bias is not None:
+        _need(bias, "linear bias", x.dtype)
+        if bias.shape[0] != weight.shape[0]:
+            raise KernelError(f"linear: a bias of {bias.shape[0]} entries for {weight.shape[0]} outputs")
+        if x.dtype == torch.float32:
+            out = linear(x, weight, out_dtype, err)
+            _call("thn_add_bias_f32", _ptr(out), _ptr(bias), out.shape[0], out.shape[1], 1.0, _stream())
+            return out
+        _need(x, "linear x")
+        _need(weight, "linear weight", x.dtype)
+        if out_dtype in (None, torch.bfloat16):
+            return torch.nn.functional.linear(x, weight, bias)
+        out = torch.mm(x, weight.t(), out_dtype=out_dtype)
+        _call("thn_add_bias_f32", _ptr(out), _ptr(bias.float()), out.shape[0], out.shape[1], 1.0, _stream())
+        return out
     _need(x, "linear x")
     _need(weight, "linear weight", x.dtype)
     if x.dim() != 2 or weight.dim() != 2 or x.shape[1] != weight.shape[1]:
@@ -751,16 +790,23 @@ def qk_norm_rope_cache(qkv, q_gain: Optional[torch.Tensor], k_gain: Optional[tor
 
 def attention_generic(q: torch.Tensor, rows: StepRows, kv: KVView, n_q: int, scale: float,
                       window: Optional[int], err: torch.Tensor, keep_first: int = 0, chunk: Optional[int] = None,
-                      exact_weights: bool = False, shape: ScoreShape = PLAIN_SCORES) -> torch.Tensor:
+                      exact_weights: bool = False, shape: ScoreShape = PLAIN_SCORES,
+                      sinks: Optional[torch.Tensor] = None) -> torch.Tensor:
     """One warp per (row, head), any sizes.  ``chunk``: a row sees only the keys of its own chunk
     of that many positions; ``exact_weights``: the softmax weights stay float32 where they
-    multiply the values; the output has ``kv.v_dim`` entries per head."""
+    multiply the values; the output has ``kv.v_dim`` entries per head.  ``sinks`` (float32
+    ``[n_q]``): the softmax's denominator of head h also holds ``exp(sinks[h])``, a term without
+    key and value."""
     _need(q, "attention q")
+    if sinks is not None:
+        _need(sinks, "attention sinks", torch.float32)
+        if sinks.shape[0] != n_q:
+            raise KernelError(f"attention: {sinks.shape[0]} sinks for {n_q} heads")
     out = torch.empty((q.shape[0], n_q * kv.v_dim), dtype=q.dtype, device=q.device)
     _call("thn_attention_generic", _ptr(out), _ptr(q), _ptr(rows.row_slot), _ptr(rows.row_pos), _ptr(kv.storage),
           _ptr(kv.block_table), kv.block_table.shape[1], kv.n_kv, kv.page_size, kv.head_dim, kv.v_dim, rows.n_rows, n_q,
           float(scale), int(window or 0), int(keep_first or 0), int(chunk or 0), int(bool(exact_weights)), *shape.args(),
-          _code(q, "attention"), _ptr(err), _stream())
+          _ptr(sinks), _code(q, "attention"), _ptr(err), _stream())
     return out
 
 
@@ -770,12 +816,19 @@ ROTARY_LAYOUTS = {"half": 0, "interleaved": 1}
 
 def qk_prepare(proj: torch.Tensor, q_gain: Optional[torch.Tensor], k_gain: Optional[torch.Tensor], norm_scope: str,
                eps: float, rotary: Optional[RotaryTables], rows: StepRows, kv: KVView, n_q: int,
-               values_are_keys: bool, write_cache: bool, err: torch.Tensor, gain_offset: float = 0.0) -> torch.Tensor:
+               values_are_keys: bool, write_cache: bool, err: torch.Tensor, gain_offset: float = 0.0,
+               value_rotary: Optional[RotaryTables] = None, proj_offset: int = 0) -> torch.Tensor:
     """From projected rows ``[q | k | v]`` (or ``[q | k]`` when the values are the keys as
     projected) to queries; keys and values go to the cache.  ``norm_scope``: "head" (an RMS norm
     per head, gains ``[head_dim]``), "projection" (one RMS norm over all heads of q and one over
     all heads of k, gains of those sizes) or None; the rotation follows ``rotary.layout``.
-    Float32 inside, one rounding at the store."""
+    Float32 inside, one rounding at the store.  ``value_rotary``: tables by which the values are
+    turned (their first ``rotary_dim`` entries, the keys' layout of pairs) before they go to the
+    cache.  ``proj_offset``: the column of ``proj`` at which ``[q | k | v]`` starts (a slice of a
+    wider projected row)."""
+    if value_rotary is not None and rotary is not None and value_rotary.layout != rotary.layout:
+        raise KernelError("qk_prepare: keys and values turn in one layout of pairs")
+    layout = rotary.layout if rotary else (value_rotary.layout if value_rotary else "half")
     _need(proj, "qk_prepare proj")
     if kv.storage.dtype != proj.dtype:
         raise KernelError(f"qk_prepare: cache is {kv.storage.dtype}, activations {proj.dtype}")
@@ -792,13 +845,19 @@ def qk_prepare(proj: torch.Tensor, q_gain: Optional[torch.Tensor], k_gain: Optio
     q = torch.empty((rows.n_rows, n_q * kv.head_dim), dtype=proj.dtype, device=proj.device)
     if values_are_keys and kv.v_dim != kv.head_dim:
         raise KernelError("qk_prepare: values that are the keys have the keys' size")
-    _call("thn_qk_prepare", _ptr(q), _ptr(proj), proj.shape[1], _ptr(q_gain) if scope else None,
+    if proj_offset < 0 or proj_offset + (n_q + kv.n_kv) * kv.head_dim + (0 if values_are_keys else kv.n_kv * kv.v_dim) > proj.shape[1]:
+        raise KernelError(f"qk_prepare: rows of {proj.shape[1]} hold no q, k, v from column {proj_offset}")
+    _call("thn_qk_prepare", _ptr(q), proj.data_ptr() + proj_offset * proj.element_size(), proj.shape[1],
+          _ptr(q_gain) if scope else None,
           _ptr(k_gain) if scope else None, scope, float(gain_offset), float(eps),
           _ptr(rotary.cos) if rotary else None, _ptr(rotary.sin) if rotary else None,
           rotary.cos.shape[0] if rotary else 0, rotary.rotary_dim if rotary else 0,
-          ROTARY_LAYOUTS[rotary.layout] if rotary else 0, int(bool(values_are_keys)), _ptr(rows.row_slot),
+          ROTARY_LAYOUTS[layout], int(bool(values_are_keys)), _ptr(rows.row_slot),
           _ptr(rows.row_pos), _ptr(kv.storage), _ptr(kv.block_table), kv.block_table.shape[1], kv.n_kv, kv.page_size,
-          kv.head_dim, kv.v_dim, rows.n_rows, n_q, int(bool(write_cache)), DTYPE_CODE[proj.dtype], _ptr(err), _stream())
+          kv.head_dim, kv.v_dim, rows.n_rows, n_q, int(bool(write_cache)),
+          _ptr(value_rotary.cos) if value_rotary else None, _ptr(value_rotary.sin) if value_rotary else None,
+          value_rotary.cos.shape[0] if value_rotary else 0, value_rotary.rotary_dim if value_rotary else 0,
+          DTYPE_CODE[proj.dtype], _ptr(err), _stream())
     return q
 
 
@@ -816,7 +875,7 @@ def prompt_attention_tile(dtype: torch.dtype, kv_head_dim: int, page_size: int, 
 def attention(q: torch.Tensor, rows: StepRows, kv: KVView, n_q: int, scale: float, window: Optional[int],
               err: torch.Tensor, tiles: Optional[RowTiles] = None, keep_first: int = 0,
               chunk: Optional[int] = None, exact_weights: bool = False,
-              shape: ScoreShape = PLAIN_SCORES) -> torch.Tensor:
+              shape: ScoreShape = PLAIN_SCORES, sinks: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Causal attention of the step's rows over the cache (which already holds the step's
     own keys).  Chooses the kernel by dtype, head size and step shape; the tensor-core
     kernels for steps of several tokens per sequence need ``tiles``.  With a window,
@@ -828,10 +887,12 @@ def attention(q: torch.Tensor, rows: StepRows, kv: KVView, n_q: int, scale: floa
     (head size 128) has one bfloat16 part only and is taken all the same: it is 2.4 to 3.6 times
     faster there than the ``mma.sync`` kernel with two parts; ``THN_ATTN_TCGEN05=0`` sends those
     prompts to the latter.  ``shape``: a position-dependent factor on a row's scores and a tanh
-    cap (:class:`ScoreShape`), taken by every kernel but the streaming decode kernel."""
+    cap (:class:`ScoreShape`), taken by every kernel but the streaming decode kernel.  ``sinks``: a
+    term ``exp(sinks[h])`` without key and value in the softmax's denominator of head h; the
+    warp-per-(row, head) kernel takes it."""
     keep_first = int(keep_first or 0) if window else 0
-    if kv.v_dim != kv.head_dim:
-        return attention_generic(q, rows, kv, n_q, scale, window, err, keep_first, chunk, exact_weights, shape)
+    if kv.v_dim != kv.head_dim or sinks is not None:
+        return attention_generic(q, rows, kv, n_q, scale, window, err, keep_first, chunk, exact_weights, shape, sinks)
     if q.dtype == torch.bfloat16 and lib().thn_attention_mma_supported(kv.head_dim, kv.page_size, n_q, kv.n_kv):
         if rows.max_q_len == 1:
             return attention_decode_bf16(q, rows, kv, n_q, scale, window, err, keep_first=keep_first, chunk=chunk,
@@ -1217,11 +1278,13 @@ SCORINGS = {"softmax": 0, "logistic": 1}
 
 
 def moe_route(logits: torch.Tensor, n_experts: int, n_groups: int, keep: int, top: int, scale: float,
-              scoring: str = "softmax") -> Routing:
+              scoring: str = "softmax", renormalise: Optional[float] = None) -> Routing:
     """Routing weights from float32 router logits (the first ``n_experts`` columns of
     ``logits``): scores by softmax over all experts or (``scoring`` "logistic") the logistic
     function of each logit, the ``keep`` best of ``n_groups`` groups of neighbours (a group's
-    score is its largest), the ``top`` best allowed experts, weights ``score * scale``."""
+    score is its largest), the ``top`` best allowed experts, weights ``score * scale``.
+    ``renormalise`` (a small number, softmax scores only): the chosen experts' scores are divided by
+    their sum plus that number first."""
     _need(logits, "moe_route logits", torch.float32)
     rows = logits.shape[0]
     if logits.shape[1] < n_experts:
@@ -1230,19 +1293,24 @@ def moe_route(logits: torch.Tensor, n_experts: int, n_groups: int, keep: int, to
     chosen = torch.empty((rows, top), dtype=torch.int32, device=logits.device)
     weight = torch.empty((rows, top), dtype=torch.float32, device=logits.device)
     _call("thn_moe_route", _ptr(dense), _ptr(chosen), _ptr(weight), _ptr(logits), logits.shape[1], rows, n_experts,
-          n_groups, keep, top, float(scale), SCORINGS[scoring], _stream())
+          n_groups, keep, top, float(scale), SCORINGS[scoring], int(renormalise is not None), float(renormalise or 0.0),
+          _stream())
     return Routing(dense, chosen, weight)
 
 
 def routed_clamped_glu(gu: torch.Tensor, routing: Routing, ff: int, shared_ff: int, limit: float, shared_limit: float,
-                       alpha: float, shared_logit: Optional[torch.Tensor] = None, logit_column: int = 0) -> torch.Tensor:
+                       alpha: float, shared_logit: Optional[torch.Tensor] = None, logit_column: int = 0,
+                       weight_at: str = "input") -> torch.Tensor:
     """Experts ``g * logistic(alpha * g) * (u + 1)`` with ``g = min(w * gate, limit)`` and
     ``u = clamp(w * up, -limit, limit)``, ``w`` the routing weight of the column's expert: the
     expert sees the token times its weight, and its projections are linear.  ``gu`` [rows,
     2 * (experts * ff + shared_ff)] holds the gates of all columns, then the ups.  The shared
     expert's columns take ``w = 1`` and ``shared_limit`` and are multiplied by
     ``logistic(shared_logit[:, logit_column])`` (no gate without ``shared_logit``); columns of an
-    expert that was not chosen are zero.  Returns [rows, experts * ff + shared_ff]."""
+    expert that was not chosen are zero.  ``weight_at`` "output": the expert sees the token itself
+    and ``w`` multiplies its activation instead.  Returns [rows, experts * ff + shared_ff]."""
+    if weight_at not in ("input", "output"):
+        raise KernelError(f"routed_clamped_glu: weight_at {weight_at!r} is neither 'input' nor 'output'")
     _need(gu, "routed_clamped_glu gu")
     rows, n_experts = routing.dense.shape
     width = n_experts * ff + shared_ff
@@ -1254,7 +1322,8 @@ def routed_clamped_glu(gu: torch.Tensor, routing: Routing, ff: int, shared_ff: i
         logit_ptr, stride = shared_logit.data_ptr() + 4 * logit_column, shared_logit.shape[1]
     out = torch.empty((rows, width), dtype=gu.dtype, device=gu.device)
     _call("thn_routed_clamped_glu", _ptr(out), _ptr(gu), _ptr(routing.dense), logit_ptr, stride, rows, n_experts, ff,
-          shared_ff, float(limit), float(shared_limit or 1.0), float(alpha), _code(gu, "routed_clamped_glu"), _stream())
+          shared_ff, float(limit), float(shared_limit or 1.0), float(alpha), int(weight_at == "output"),
+          _code(gu, "routed_clamped_glu"), _stream())
     return out
 
 
@@ -1274,6 +1343,191 @@ def routed_gelu(u: torch.Tensor, routing: Routing, ff: int, shared_ff: int,
     out = torch.empty_like(u)
     _call("thn_routed_gelu", _ptr(out), _ptr(u), _ptr(routing.dense), logit_ptr, stride, rows, n_experts, ff, shared_ff,
           _code(u, "routed_gelu"), _stream())
+    return out
+
+
+# ------------------------------------------------------------------ hyper-connections
+
+
+@dataclass
+class StreamNumbers:
+    """The numbers of one sublayer's hyper-connection (float32, on the device): ``read`` [streams]
+    (how the sublayer's input is mixed from the streams), ``mix`` [streams, streams] ([from, to]) and
+    ``write`` [streams] (how the streams are remixed and the sublayer's output added)."""
+
+    read: torch.Tensor
+    mix: torch.Tensor
+    write: torch.Tensor
+
+
+def hyper_norm(streams: Optional[torch.Tensor], n_streams: int, dtype: torch.dtype, *,
+               start: Optional[torch.Tensor] = None, y: Optional[torch.Tensor] = None,
+               written: Optional[StreamNumbers] = None, read: Optional[torch.Tensor] = None,
+               gain: Optional[torch.Tensor] = None, eps: float = 1.0) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+    """Between two sublayers over a residual stream of ``n_streams`` copies kept in float32
+    (``streams`` [rows, n_streams * width], updated in place): the write of the sublayer that
+    produced ``y`` (``X'_i = sum_j mix[j, i] X_j + write[i] y``), then the read of the next one and
+    its RMS norm, ``n = u / sqrt(mean(u^2) + eps) * gain`` with ``u = sum_j read[j] X'_j`` and
+    ``gain`` float32 of one entry or ``[width]``.  ``start`` (float32 [rows, width]) instead of
+    ``streams``: every stream starts as that row.  Returns ``(streams, n)``; ``n`` is None
+    without ``read``."""
+    if (streams is None) == (start is None):
+        raise KernelError("hyper_norm: either the streams or the row they start as")
+    if start is not None:
+        _need(start, "hyper_norm start", torch.float32)
+        streams = torch.empty((start.shape[0], n_streams * start.shape[1]), dtype=torch.float32, device=start.device)
+    _need(streams, "hyper_norm streams", torch.float32)
+    rows = streams.shape[0]
+    if streams.dim() != 2 or streams.shape[1] % n_streams:
+        raise KernelError(f"hyper_norm: streams {tuple(streams.shape)} are not {n_streams} rows side by side")
+    width = streams.shape[1] // n_streams
+    if y is not None:
+        _need(y, "hyper_norm y", dtype)
+        if written is None or tuple(y.shape) != (rows, width):
+            raise KernelError(f"hyper_norm: y {tuple(y.shape)} for rows of {width}, with its numbers")
+        _need(written.mix, "hyper_norm mix", torch.float32)
+        _need(written.write, "hyper_norm write", torch.float32)
+        if written.mix.numel() != n_streams * n_streams or written.write.numel() != n_streams:
+            raise KernelError("hyper_norm: the numbers of the write do not fit the streams")
+    n = None
+    if read is not None:
+        _need(read, "hyper_norm read", torch.float32)
+        _need(gain, "hyper_norm gain", torch.float32)
+        if read.numel() != n_streams or gain.numel() not in (1, width):
+            raise KernelError("hyper_norm: the numbers of the read or the gain do not fit")
+        n = torch.empty((rows, width), dtype=dtype, device=streams.device)
+    _call("thn_hyper_norm", _ptr(n), _ptr(streams), _ptr(start), _ptr(y), _ptr(written.mix) if y is not None else None,
+          _ptr(written.write) if y is not None else None, _ptr(read), _ptr(gain),
+          int(gain is not None and gain.numel() != 1), float(eps), rows, width, n_streams, DTYPE_CODE[dtype], _stream())
+    return streams, n
+
+
+# ------------------------------------------------------------------ linear attention, selective scan
+
+
+def linear_attention(proj: torch.Tensor, offsets: Tuple[int, int, int], state: torch.Tensor, rows: StepRows,
+                     n_heads: int, key_dim: int, value_dim: int, *, decay: Optional[torch.Tensor] = None,
+                     gate: Optional[torch.Tensor] = None, gate_bias: Optional[torch.Tensor] = None, tau: float = 1.0,
+                     q_scale: float = 1.0, silu_inputs: bool = False) -> torch.Tensor:
+    """Linear attention with a decayed matrix state over a step's rows: per head
+    ``S <- diag(a) S + k v^T``, ``o = S^T q * q_scale`` from the state the sequences' earlier steps
+    left.  ``proj`` rows hold q, k (``heads * key_dim``) and v (``heads * value_dim``) from the
+    columns ``offsets``; with ``silu_inputs`` they pass silu first.  The decay is ``decay`` (float32
+    ``[heads]``, one constant per head) or, per token and key channel,
+    ``logistic(gate + gate_bias) ** (1 / tau)`` with ``gate`` float32 ``[rows, >= heads * key_dim]``.
+    ``state`` float32 [slots, heads, value_dim, key_dim] is read and updated.  Returns the read-out,
+    float32 [rows, heads, value_dim]."""
+    _need(proj, "linear_attention proj")
+    _need(state, "linear_attention state", torch.float32)
+    if (decay is None) == (gate is None):
+        raise KernelError("linear_attention: either a constant decay per head or a gate per token")
+    if proj.shape[0] != rows.n_rows or tuple(state.shape[1:]) != (n_heads, value_dim, key_dim):
+        raise KernelError(f"linear_attention: proj {tuple(proj.shape)}, state {tuple(state.shape)} do not fit {n_heads} "
+                          f"heads of {key_dim} x {value_dim} over {rows.n_rows} rows")
+    if decay is not None:
+        _need(decay, "linear_attention decay", torch.float32)
+        if decay.shape[0] != n_heads:
+            raise KernelError(f"linear_attention: {decay.shape[0]} decays for {n_heads} heads")
+    else:
+        _need(gate, "linear_attention gate", torch.float32)
+        if gate.shape[0] != rows.n_rows or gate.shape[1] < n_heads * key_dim:
+            raise KernelError(f"linear_attention: gate {tuple(gate.shape)}")
+        if gate_bias is not None:
+            _need(gate_bias, "linear_attention gate bias", torch.float32)
+            if gate_bias.shape[0] != n_heads * key_dim:
+                raise KernelError(f"linear_attention: gate bias {tuple(gate_bias.shape)}")
+    o = torch.empty((rows.n_rows, n_heads, value_dim), dtype=torch.float32, device=proj.device)
+    _call("thn_linear_attention", _ptr(o), _ptr(state), _ptr(proj), proj.shape[1], int(offsets[0]), int(offsets[1]),
+          int(offsets[2]), _ptr(decay), _ptr(gate), gate.shape[1] if gate is not None else 0, _ptr(gate_bias), float(tau),
+          _ptr(rows.cu_seqlens), _ptr(rows.slots), rows.n_seqs, n_heads, key_dim, value_dim, float(q_scale),
+          0 if decay is not None else 1, int(bool(silu_inputs)), _code(proj, "linear_attention"), _stream())
+    return o
+
+
+def causal_conv(proj: torch.Tensor, offset: int, channels: int, weight: torch.Tensor, bias: Optional[torch.Tensor],
+                ring: torch.Tensor, rows: StepRows, seq_lens: torch.Tensor) -> torch.Tensor:
+    """A short causal convolution per channel over time, then silu: ``out[t, c] = silu(bias[c] +
+    sum_j weight[c, j] raw[t - (taps - 1) + j, c])`` with zeros before a sequence's start; the raw
+    inputs are the columns ``[offset, offset + channels)`` of ``proj``.  Inputs of earlier steps
+    come from ``ring`` [slots, taps, channels] (position p at ``p mod taps``), which
+    :func:`conv_ring_update` brings up to date after this call; ``seq_lens`` holds the tokens each
+    slot held before the step."""
+    _need(proj, "causal_conv proj")
+    _need(weight, "causal_conv weight", torch.float32)
+    _need(ring, "causal_conv ring", proj.dtype)
+    taps = weight.shape[1]
+    if tuple(weight.shape) != (channels, taps) or tuple(ring.shape[1:]) != (taps, channels) or proj.shape[0] != rows.n_rows \
+            or offset + channels > proj.shape[1]:
+        raise KernelError(f"causal_conv: proj {tuple(proj.shape)}, weight {tuple(weight.shape)}, ring {tuple(ring.shape)}")
+    if bias is not None:
+        _need(bias, "causal_conv bias", torch.float32)
+    out = torch.empty((rows.n_rows, channels), dtype=proj.dtype, device=proj.device)
+    _call("thn_causal_conv", _ptr(out), _ptr(proj), proj.shape[1], int(offset), _ptr(weight), _ptr(bias), _ptr(ring),
+          _ptr(rows.row_slot), _ptr(rows.row_pos), _ptr(seq_lens), rows.n_rows, channels, taps, _code(proj, "causal_conv"),
+          _stream())
+    return out
+
+
+def conv_ring_update(ring: torch.Tensor, proj: torch.Tensor, offset: int, rows: StepRows, seq_lens: torch.Tensor) -> None:
+    """The step's last raw inputs (at most ``taps`` per sequence) go into ``ring``."""
+    _need(ring, "conv_ring_update ring", proj.dtype)
+    _call("thn_conv_ring_update", _ptr(ring), _ptr(proj), proj.shape[1], int(offset), _ptr(rows.cu_seqlens), _ptr(rows.slots),
+          _ptr(seq_lens), rows.n_seqs, ring.shape[2], ring.shape[1], _code(proj, "conv_ring_update"), _stream())
+
+
+def selective_scan(x: torch.Tensor, dt_pre: torch.Tensor, dt_bias: torch.Tensor, bc: torch.Tensor, a: torch.Tensor,
+                   d: torch.Tensor, gate: torch.Tensor, gate_offset: int, state: torch.Tensor, rows: StepRows) -> torch.Tensor:
+    """The selective scan over a step's rows: per channel c and state entry n
+    ``S[c, n] <- exp(dt_c a[c, n]) S[c, n] + dt_c x_c B_n``, ``y_c = (sum_n S[c, n] C_n + d_c x_c) *
+    silu(z_c)`` with ``dt = softplus(dt_pre + dt_bias)`` (float32), ``bc`` rows ``[B | C]`` and z the
+    columns of ``gate`` from ``gate_offset``.  ``state`` float32 [slots, channels, n] is read and
+    updated.  Returns y [rows, channels] of the activation type."""
+    _need(x, "selective_scan x")
+    _need(dt_pre, "selective_scan dt", torch.float32)
+    _need(dt_bias, "selective_scan dt bias", torch.float32)
+    _need(bc, "selective_scan bc", x.dtype)
+    _need(a, "selective_scan a", torch.float32)
+    _need(d, "selective_scan d", torch.float32)
+    _need(gate, "selective_scan gate", x.dtype)
+    _need(state, "selective_scan state", torch.float32)
+    n_rows, channels = x.shape
+    n_state = a.shape[1]
+    if n_rows != rows.n_rows or tuple(dt_pre.shape) != (n_rows, channels) or tuple(a.shape) != (channels, n_state) \
+            or bc.shape[0] != n_rows or bc.shape[1] < 2 * n_state or tuple(state.shape[1:]) != (channels, n_state) \
+            or gate.shape[0] != n_rows or gate_offset + channels > gate.shape[1] or d.shape[0] != channels \
+            or dt_bias.shape[0] != channels:
+        raise KernelError(f"selective_scan: x {tuple(x.shape)}, dt {tuple(dt_pre.shape)}, bc {tuple(bc.shape)}, a "
+                          f"{tuple(a.shape)}, state {tuple(state.shape)}, gate {tuple(gate.shape)} from {gate_offset}")
+    y = torch.empty_like(x)
+    _call("thn_selective_scan", _ptr(y), _ptr(state), _ptr(x), _ptr(dt_pre), _ptr(dt_bias), _ptr(bc), bc.shape[1], _ptr(a),
+          _ptr(d), gate.data_ptr() + gate_offset * gate.element_size(), gate.shape[1], _ptr(rows.cu_seqlens),
+          _ptr(rows.slots), rows.n_seqs, channels, n_state, _code(x, "selective_scan"), _stream())
+    return y
+
+
+def rotate_gate(a: torch.Tensor, gate: torch.Tensor, gate_offset: int, n_heads: int, size: int,
+                rotary: Optional[RotaryTables], rows: StepRows, err: Optional[torch.Tensor], scale: float = 1.0,
+                out: Optional[torch.Tensor] = None, out_offset: int = 0) -> torch.Tensor:
+    """``a`` [rows, heads * size], every head turned back by its row's position (the inverse of the
+    turn that :func:`qk_prepare` gave the values; ``rotary`` None: no turn), times
+    ``logistic(gate[:, gate_offset : gate_offset + heads * size])`` times ``scale``.  With ``out`` the
+    result goes to its columns from ``out_offset``."""
+    _need(a, "rotate_gate a")
+    _need(gate, "rotate_gate gate", a.dtype)
+    n_rows, width = a.shape
+    if width != n_heads * size or gate.shape[0] != n_rows or gate_offset + width > gate.shape[1]:
+        raise KernelError(f"rotate_gate: a {tuple(a.shape)}, gate {tuple(gate.shape)} from {gate_offset}")
+    if out is None:
+        out, out_offset = torch.empty_like(a), 0
+    else:
+        _need(out, "rotate_gate out", a.dtype)
+        if out.shape[0] != n_rows or out_offset < 0 or out_offset + width > out.shape[1]:
+            raise KernelError(f"rotate_gate: out {tuple(out.shape)} has no room for {width} columns from {out_offset}")
+    _call("thn_rotate_gate", out.data_ptr() + out_offset * out.element_size(), out.shape[1], _ptr(a),
+          gate.data_ptr() + gate_offset * gate.element_size(), gate.shape[1], _ptr(rotary.cos) if rotary else None,
+          _ptr(rotary.sin) if rotary else None, rotary.cos.shape[0] if rotary else 0, rotary.rotary_dim if rotary else 0,
+          ROTARY_LAYOUTS[rotary.layout] if rotary else 0, _ptr(rows.row_pos), n_rows, n_heads, size, float(scale),
+          _code(a, "rotate_gate"), _ptr(err), _stream())
     return out
 
 
@@ -1320,5 +1574,5 @@ def gather_i32(src: torch.Tensor, index: torch.Tensor, out: Optional[torch.Tenso
 __all__ = [
     "KernelError", "KernelLibraryError", "KVView", "RotaryTables", "RowTiles", "StepRows", "row_tiles_of", "prompt_attention_tile", "linear_stream", "linear_swiglu", "linear_tcgen05", "add_rmsnorm", "advance",
     "ROW_TILE", "attention", "attention_decode_bf16", "attention_generic", "attention_prefill_bf16", "attention_prefill_tcgen05", "decode_splits", "choose_tokens", "gather_i32", "gather_rows", "lib", "linear", "new_error_word",
-    "qk_norm_rope_cache", "qk_prepare", "Gain", "STREAM_AS_IS", "residual_norm", "gather_rows_scaled", "logistic_gate", "latent_norm", "latent_assemble", "mlstm", "mlstm_column_blocks", "set_mlstm_kernel", "Routing", "moe_route", "routed_gelu", "gated_head_norm", "clamped_glu", "routed_clamped_glu", "polynorm", "scale_", "ScoreShape", "PLAIN_SCORES", "DeltaShape", "delta_rule", "qkv_attention", "raise_on_device_error", "rmsnorm", "rope_table", "scatter_i32", "step_rows", "swiglu",
+    "qk_norm_rope_cache", "qk_prepare", "Gain", "STREAM_AS_IS", "residual_norm", "gather_rows_scaled", "logistic_gate", "latent_norm", "latent_assemble", "mlstm", "mlstm_column_blocks", "set_mlstm_kernel", "Routing", "moe_route", "routed_gelu", "gated_head_norm", "clamped_glu", "routed_clamped_glu", "polynorm", "scale_", "ScoreShape", "PLAIN_SCORES", "DeltaShape", "delta_rule", "qkv_attention", "raise_on_device_error", "rmsnorm", "StreamNumbers", "hyper_norm", "linear_attention", "causal_conv", "conv_ring_update", "selective_scan", "rotate_gate", "rope_table", "scatter_i32", "step_rows", "swiglu",
 ]

@@ -23,6 +23,16 @@ feed-forward half may be absent.  The pending output again travels as a :class:`
 block, default 1; the feed-forward may be absent).  The two outputs travel as one
 :class:`Branch` with its second tensor and its factor, so that "add both, times the factor, into
 the stream, norm of the sum" is one kernel at the next layer's norm or at the model's last.
+
+``hyper_connections``: the residual stream is ``streams`` copies ``X_0 .. X_(s-1)`` in float32,
+all equal to the embedding's row at the start.  A sublayer f with the numbers ``read[s]``,
+``mix[s, s]`` ([from, to]) and ``write[s]`` does ``u = sum_j read[j] X_j``, ``y = f(norm(u))``,
+``X'_i = sum_j mix[j, i] X_j + write[i] y``; a layer is its mixer as such a sublayer, then its
+feed-forward where it has one.  The pending output travels as a :class:`Branch` with the numbers
+of its write, so that "write of the last sublayer, read of the next, its norm" is one kernel
+(:func:`ops.hyper_norm`), also into the model's last norm, which reads the sum of the copies.
+Without the numbers' tensors (``connections`` False) it is one copy and the plain
+``x <- x + f(norm(x))``.
 """
 
 from __future__ import annotations
@@ -33,7 +43,8 @@ import torch
 
 from ..cache.sequence_cache import CacheNeed
 from ..config.base import PartSpec, ScheduleEntry
-from ..weights.loader import TensorSpec
+from .. import ops
+from ..weights.loader import GAIN, TensorSpec
 from .registry import part_class, register_part
 from .runtime import Branch, HostBatch, Runtime, StepContext
 
@@ -152,3 +163,57 @@ class ParallelBlock(Block):
         a = self.mixer.forward(n, ctx, entry)
         f = self.ffn.forward(n, ctx) if self.ffn is not None else None
         return h, Branch(a, None, f, self.factor)
+
+
+@register_part("block", "hyper_connections")
+class HyperConnectionBlock(Block):
+    MEMBERS = {"norm_mixer": "norm", "mixer": "mixer", "norm_ffn": "norm", "ffn": "ffn"}
+    SUBLAYERS = ("mixer", "ffn")
+
+    @classmethod
+    def tensor_specs(cls, spec: PartSpec) -> List[TensorSpec]:
+        specs = super().tensor_specs(spec)
+        s = int(spec.params.get("streams") or 1)
+        if spec.params.get("connections", True):
+            for name in cls.SUBLAYERS:
+                if spec.params.get(name) is None:
+                    continue
+                specs += [TensorSpec(spec.tensors[f"{name}.read"], (s,), GAIN, init="stream_read"),
+                          TensorSpec(spec.tensors[f"{name}.write"], (s,), GAIN),
+                          TensorSpec(spec.tensors[f"{name}.mix"], (s, s), GAIN, init="stream_mix")]
+        return specs
+
+    def __init__(self, spec: PartSpec, runtime: Runtime):
+        super().__init__(spec, runtime)
+        self.streams = s = int(spec.params.get("streams") or 1)
+        self.numbers = {}
+        f32 = lambda t: t.to(torch.float32).contiguous()
+        for name in self.SUBLAYERS:
+            if spec.params.get(name) is None:
+                continue
+            if spec.params.get("connections", True):
+                self.numbers[name] = ops.StreamNumbers(f32(runtime.tensor(spec, f"{name}.read")),
+                                                       f32(runtime.tensor(spec, f"{name}.mix")),
+                                                       f32(runtime.tensor(spec, f"{name}.write")))
+            else:
+                if s != 1:
+                    raise ValueError("hyper_connections: several streams need the numbers that connect them")
+                one = torch.ones(1, dtype=torch.float32, device=runtime.device)
+                self.numbers[name] = ops.StreamNumbers(one, one.reshape(1, 1), one)
+
+    def forward(self, h: torch.Tensor, d, ctx: StepContext, entry: ScheduleEntry):
+        if h.dtype != torch.float32:
+            raise TypeError("hyper_connections: the residual stream must start in float32 (an embedding with stream 'float32')")
+        own = self.numbers["mixer"]
+        if d is None:           # the model's first layer: every copy starts as the embedding's row
+            X, n = self.norm_mixer.stream_norm(None, self.streams, start=h, read=own.read)
+        elif isinstance(d, Branch) and d.write is not None:
+            X, n = self.norm_mixer.stream_norm(h, self.streams, y=d.tensor, written=d.write, read=own.read)
+        else:
+            raise TypeError("hyper_connections: a pending branch must carry the numbers of its write")
+        a = self.mixer.forward(n, ctx, entry)
+        if self.ffn is None:
+            return X, Branch(a, write=own)
+        after = self.numbers["ffn"]
+        X, n = self.norm_ffn.stream_norm(X, self.streams, y=a, written=own, read=after.read)
+        return X, Branch(self.ffn.forward(n, ctx), write=after)

@@ -29,7 +29,11 @@ and up projections of all experts are one product over ``x`` and the activation 
 the projected values by ``w`` before the clamps; one down-projection over all experts' columns
 sums the chosen ones.  With ``shared_ff`` a shared expert with a limit of its own
 (``shared_limit``) runs for every token on the token itself and is added times
-``logistic(shared_gate(x))``."""
+``logistic(shared_gate(x))`` (``shared_gated`` False: added as it is).  ``scoring`` "softmax": the
+scores are a softmax over all experts instead; ``renormalise`` (a small number): the chosen
+experts' scores are divided by their sum plus that number; ``weight_at`` "output": an expert sees
+the token itself and its output is weighted (the weight then multiplies the activation, ahead of
+the one down-projection over all columns)."""
 
 from __future__ import annotations
 
@@ -182,6 +186,13 @@ class RoutedClampedExperts:
             raise ValueError(f"routed_clamped_experts: top {self.top} of {self.n_experts} experts")
         self.limit, self.slope = float(p["limit"]), float(p["slope"])
         self.shared_limit = float(p.get("shared_limit") or self.limit)
+        self.scoring = str(p.get("scoring", "logistic"))
+        self.renormalise = None if p.get("renormalise") is None else float(p["renormalise"])
+        self.weight_at = str(p.get("weight_at", "input"))
+        if self.scoring not in ops.SCORINGS or self.weight_at not in ("input", "output") \
+                or (self.renormalise is not None and self.scoring != "softmax"):
+            raise ValueError(f"routed_clamped_experts: scoring {self.scoring!r}, weight_at {self.weight_at!r}, "
+                             f"renormalise {self.renormalise!r}")
         self.shared_gated = bool(self.shared_ff) and bool(p.get("shared_gated", True))
         gates = [runtime.tensor(spec, f"gate.{e}") for e in range(self.n_experts)]
         ups = [runtime.tensor(spec, f"up.{e}") for e in range(self.n_experts)]
@@ -200,8 +211,8 @@ class RoutedClampedExperts:
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
         err = getattr(ctx, "err", None)
         z = ops.linear(x, self.w_route, out_dtype=torch.float32, err=err)
-        routing = ops.moe_route(z, self.n_experts, 1, 1, self.top, 1.0, scoring="logistic")
+        routing = ops.moe_route(z, self.n_experts, 1, 1, self.top, 1.0, scoring=self.scoring, renormalise=self.renormalise)
         gu = ops.linear(x, self.w_gate_up, err=err)
         y = ops.routed_clamped_glu(gu, routing, self.ff, self.shared_ff, self.limit, self.shared_limit, self.slope,
-                                   z if self.shared_gated else None, self.n_experts)
+                                   z if self.shared_gated else None, self.n_experts, weight_at=self.weight_at)
         return ops.linear(y, self.w_down, err=err)

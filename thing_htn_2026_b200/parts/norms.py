@@ -11,7 +11,10 @@ added (norms on both sides of a sublayer), in the same kernel.  ``groups`` (defa
 stream only): the row is split into that many equal consecutive parts, each divided by its own
 ``sqrt(mean(part^2) + eps)``, and the whole is multiplied by the gain.  ``add_forward`` takes a
 :class:`Branch` as well: its second tensor and its factor are added in the same kernel,
-``h <- h + factor * (d + d')``.
+``h <- h + factor * (d + d')``.  ``gain`` "scalar": the gain is one number (a tensor without
+axes) for all coordinates.  ``stream_norm`` serves a residual stream of several copies
+(hyper-connections, :func:`ops.hyper_norm`): the pending write of the sublayer before, the read of
+the next one and this norm of what was read, in one kernel.
 
 ``layernorm``: ``(x - mean) / sqrt(var + eps) * w + b`` with the variance as the mean of the
 squared deviations, over a float32 stream only.  Besides the calls above it has ``read`` and
@@ -37,7 +40,8 @@ class RMSNorm:
     @classmethod
     def tensor_specs(cls, spec: PartSpec) -> List[TensorSpec]:
         init = "zero_centered" if float(spec.params.get("gain_offset", 0.0)) else None
-        return [TensorSpec(spec.tensors["weight"], (int(spec.params["size"]),), GAIN, init=init)]
+        shape = () if spec.params.get("gain") == "scalar" else (int(spec.params["size"]),)
+        return [TensorSpec(spec.tensors["weight"], shape, GAIN, init=init)]
 
     def __init__(self, spec: PartSpec, runtime: Runtime):
         self.size = int(spec.params["size"])
@@ -49,10 +53,34 @@ class RMSNorm:
             raise ValueError(f"rmsnorm: {self.groups} groups must divide the size {self.size} and need a float32 stream")
         self.dtype = runtime.dtype
         self.gain = runtime.tensor(spec, "weight")
+        self.scalar_gain = spec.params.get("gain") == "scalar"
+        if self.scalar_gain:
+            if not self.float32_stream or self.offset or self.groups != 1:
+                raise ValueError("rmsnorm: a gain of one number goes with a float32 stream, no offset and no groups")
+            self.gain32 = self.gain.to(torch.float32).reshape(1).contiguous()
+            self._ones = {}
+            return
+        self.gain32 = self.gain.to(torch.float32).contiguous()
+        self._ones = {}
         if self.float32_stream or self.offset:
             self.as_gain = ops.Gain(self.gain.to(torch.float32).contiguous(), self.offset, self.eps, groups=self.groups)
 
+    def stream_norm(self, streams: Optional[torch.Tensor], n_streams: int, *, start: Optional[torch.Tensor] = None,
+                    y: Optional[torch.Tensor] = None, written=None, read: Optional[torch.Tensor] = None):
+        """Over ``n_streams`` copies of the residual stream: the write of the sublayer that produced
+        ``y`` (``written``: its :class:`ops.StreamNumbers`), then the read with the numbers ``read``
+        (None: the sum of the copies) and this norm of it.  ``start``: the row every copy starts as.
+        Returns (streams, normalised read)."""
+        if read is None:
+            if n_streams not in self._ones:
+                self._ones[n_streams] = torch.ones(n_streams, dtype=torch.float32, device=self.gain32.device)
+            read = self._ones[n_streams]
+        return ops.hyper_norm(streams, n_streams, self.dtype, start=start, y=y, written=written, read=read,
+                              gain=self.gain32, eps=self.eps)
+
     def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if self.scalar_gain:
+            return self.stream_norm(x, 1)[1]
         if self.float32_stream or self.offset:
             if x.dtype == torch.float32:
                 return ops.residual_norm(x, None, None, self.as_gain, self.dtype)[1]

@@ -31,12 +31,15 @@ class Branch:
     it passes before the add (None: it is added as it is).  Blocks hand it on in place of a bare
     tensor when the add is to be fused into the next norm.  ``second``: the output of a sublayer
     that ran beside the first on the same input, added with it; ``factor``: what multiplies
-    the branch as it is added."""
+    the branch as it is added.  ``write``: over a residual stream of several copies
+    (hyper-connections), the numbers (:class:`ops.StreamNumbers`) by which the sublayer that
+    produced the tensor remixes the copies and adds its output to each."""
 
     tensor: torch.Tensor
     norm: Optional[object] = None
     second: Optional[torch.Tensor] = None
     factor: float = 1.0
+    write: Optional[object] = None
 
 
 @dataclass(frozen=True)

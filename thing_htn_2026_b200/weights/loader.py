@@ -41,7 +41,8 @@ TABLE = "table"     # integer table
 
 @dataclass(frozen=True)
 class TensorSpec:
-    """``role`` decides the precision a tensor is held in; ``init`` names the rule that draws
+    """``shape`` may hold -1 for an axis whose size only the checkpoint gives (a tensor's shape is
+    then the one place that size is written); ``role`` decides the precision a tensor is held in; ``init`` names the rule that draws
     it in the random-weights mode (None: the role's default, see weights/random_init.py);
     ``copies`` are other checkpoint names that may store the same tensor once more."""
 
@@ -105,6 +106,11 @@ def held_dtype(stored: torch.dtype, role: str, compute_dtype: torch.dtype) -> to
     return torch.float32 if stored in (torch.float32, torch.float64) else compute_dtype
 
 
+def shape_fits(found: Sequence[int], declared: Sequence[int]) -> bool:
+    """Whether a stored shape is the declared one, -1 in the declaration standing for any size."""
+    return len(found) == len(declared) and all(d == -1 or f == d for f, d in zip(found, declared))
+
+
 def check_names(where: str, specs: Dict[str, TensorSpec], found: Dict[str, Tuple[int, ...]],
                 ignored: Sequence[str] = (), strict: bool = False) -> List[str]:
     """Raises the one :class:`WeightError`, or returns the undeclared names (copies and
@@ -114,9 +120,9 @@ def check_names(where: str, specs: Dict[str, TensorSpec], found: Dict[str, Tuple
     unexpected = [n for n in found if n not in specs and n not in copies
                   and not any(fnmatch.fnmatchcase(n, pattern) for pattern in ignored)]
     wrong = [(n, tuple(found[n]), tuple(s.shape)) for n, s in specs.items()
-             if n in found and tuple(found[n]) != tuple(s.shape)]
+             if n in found and not shape_fits(tuple(found[n]), tuple(s.shape))]
     wrong += [(c, tuple(found[c]), tuple(s.shape)) for c, s in copies.items()
-              if c in found and tuple(found[c]) != tuple(s.shape)]
+              if c in found and not shape_fits(tuple(found[c]), tuple(s.shape))]
     if missing or wrong or (strict and unexpected):
         raise WeightError(where, missing, unexpected, wrong)
     return unexpected

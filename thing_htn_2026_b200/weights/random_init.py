@@ -74,11 +74,35 @@ def _polynomial(t, generator, matrix_std, gain_std):
     return t.uniform_(-1.0, 1.0, generator=generator).mul_(0.7)
 
 
+def _stream_read(t, generator, matrix_std, gain_std):
+    """How a sublayer reads several copies of the stream: weights around one over their number."""
+    return t.normal_(0.0, gain_std, generator=generator).add_(1.0).div_(max(1, t.numel()))
+
+
+def _stream_mix(t, generator, matrix_std, gain_std):
+    """How the copies of the stream are remixed: around the identity."""
+    return t.normal_(0.0, gain_std, generator=generator).add_(torch.eye(t.shape[0], dtype=t.dtype, device=t.device))
+
+
+def _sink(t, generator, matrix_std, gain_std):
+    """A softmax's sink logit: of the order of the scores it stands beside."""
+    return t.normal_(0.0, 1.0, generator=generator)
+
+
+def _log_spread(t, generator, matrix_std, gain_std):
+    """Logarithms of the decay rates of a state-space layer: ln(1 .. n) along the state axis, jittered."""
+    n = t.shape[-1]
+    base = torch.arange(1, n + 1, dtype=torch.float32, device=t.device).log().to(t.dtype)
+    return t.normal_(0.0, gain_std, generator=generator).add_(base)
+
+
 # How a tensor is drawn, by the name in ``TensorSpec.init``.  ``fill(t, generator, matrix_std,
 # gain_std)`` fills ``t`` (float32 on the CPU, the held dtype on a device) in place.
 INITIALIZERS: Dict[str, Callable] = {"normal": _normal, "one_plus_normal": _one_plus_normal, "zeros": _zeros,
                                      "zero_centered": _zero_centered, "conv_taps": _conv_taps, "log_rate": _log_rate,
-                                     "unit_normal": _unit_normal, "small_normal": _small_normal, "gate_bias": _gate_bias, "polynomial": _polynomial}
+                                     "unit_normal": _unit_normal, "small_normal": _small_normal, "gate_bias": _gate_bias, "polynomial": _polynomial,
+                                     "stream_read": _stream_read, "stream_mix": _stream_mix, "sink": _sink,
+                                     "log_spread": _log_spread}
 # The rule of a spec that names none, by its role.
 ROLE_INIT = {MATRIX: "normal", GAIN: "one_plus_normal", TABLE: "zeros"}
 
@@ -93,6 +117,9 @@ def register_initializer(name: str, fill: Callable) -> None:
 
 def _draw(spec: TensorSpec, generator: torch.Generator, device, matrix_std: float, gain_std: float,
           dtype: torch.dtype) -> torch.Tensor:
+    if any(n < 0 for n in spec.shape):
+        raise ValueError(f"{spec.name}: shape {list(spec.shape)} leaves a size to the checkpoint; random weights need "
+                         f"it in the configuration")
     rule = spec.init or ROLE_INIT.get(spec.role)
     if rule not in INITIALIZERS:
         raise KeyError(f"{spec.name}: no initializer named '{rule}' (role '{spec.role}'); known: "
