@@ -57,7 +57,7 @@ MAMBA = "mamba1"
 
 EXPERT_GATE_SLOPE = 1.702
 ROUTER_SUM_FLOOR = 1e-20
-MAX_STREAMS = 8
+MAX_STREAMS = 16
 
 
 def _section(data: Mapping[str, Any], key: str, where: str) -> Mapping[str, Any]:
@@ -212,9 +212,11 @@ class DubazenConfig(ModelConfig):
         position = None
         if rot["dims"]:
             position = PartSpec("rope", {"head_dim": left["dim"], "rotary_dim": rot["dims"], "theta": float(rot["base"]),
-                                         "layout": "half", "frequency_precision": "float64"})
+                                         "layout": "half", "frequency_precision": "float64",
+                                         "angle_precision": "float64"})
         value_position = PartSpec("rope", {"head_dim": left["vdim"], "rotary_dim": left["vdim"], "theta": float(rot["base"]),
-                                           "layout": "half", "frequency_precision": "float64"})
+                                           "layout": "half", "frequency_precision": "float64",
+                                           "angle_precision": "float64"})
         lt = {key: f"{prefix}mix.left.{name}" for key, name in (
             ("q_proj", "q"), ("k_proj", "k"), ("v_proj", "v"), ("o_proj", "o"), ("q_bias", "q.b"), ("k_bias", "k.b"),
             ("v_bias", "v.b"), ("o_bias", "o.b"), ("sink", "sink"), ("g_proj", "g"))}

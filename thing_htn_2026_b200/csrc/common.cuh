@@ -131,6 +131,20 @@ template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(flo
 
 template <typename T> __device__ __forceinline__ float rnd(float v) { return to_f32<T>(from_f32<T>(v)); }
 
+// Transcendentals of the recurrent layers.  On the true 32-bit path (T = float) they are computed
+// in double and rounded once: a float32 expf leans one way by a fraction of an ulp, and a decay
+// that multiplies a state a thousand times over carries that lean into the logits.  With
+// bfloat16 activations the float32 functions are exact enough by a wide margin.
+template <typename T> __device__ __forceinline__ float exp_of(float x) { return expf(x); }
+template <> __device__ __forceinline__ float exp_of<float>(float x) { return (float)exp((double)x); }
+template <typename T> __device__ __forceinline__ float silu_of(float x) { return x / (1.0f + expf(-x)); }
+template <> __device__ __forceinline__ float silu_of<float>(float x) { return (float)((double)x / (1.0 + exp(-(double)x))); }
+// softplus(x) = ln(1 + e^x)
+template <typename T> __device__ __forceinline__ float softplus_of(float x) { return x > 20.f ? x : log1pf(expf(x)); }
+template <> __device__ __forceinline__ float softplus_of<float>(float x) {
+    return x > 40.f ? x : (float)log1p(exp((double)x));
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -21,7 +21,7 @@
 
 namespace {
 
-constexpr int kMaxStreams = 8;
+constexpr int kMaxStreams = 16;
 constexpr int kThreads = 256;
 
 struct HyperNumbers {

@@ -28,11 +28,15 @@ constexpr int kLanes = 8;
 constexpr int kColumns = 16;                  // columns of S per block
 constexpr int kThreads = kLanes * kColumns;   // 128
 
-__device__ __forceinline__ float silu_f(float x) { return x / (1.0f + expf(-x)); }
-
-// ln(logistic(z)) = -softplus(-z), without overflow
-__device__ __forceinline__ float log_logistic(float z) {
-    return z >= 0.f ? -log1pf(expf(-z)) : z - log1pf(expf(z));
+// logistic(z)^(1 / tau) = exp(-softplus(-z) / tau), without overflow; in double on the 32-bit path
+template <typename T> __device__ __forceinline__ float logistic_power(float z, float inv_tau) {
+    const float log_logistic = z >= 0.f ? -log1pf(expf(-z)) : z - log1pf(expf(z));
+    return expf(log_logistic * inv_tau);
+}
+template <> __device__ __forceinline__ float logistic_power<float>(float z, float inv_tau) {
+    const double x = (double)z;
+    const double log_logistic = x >= 0.0 ? -log1p(exp(-x)) : x - log1p(exp(x));
+    return (float)exp(log_logistic * (double)inv_tau);
 }
 
 template <typename T, int PER, int MODE, bool SILU>
@@ -79,13 +83,13 @@ __global__ void __launch_bounds__(kThreads) linear_attention_kernel(
     if (row0 < row1) THN_LA_LOAD(row0, kc, qc, ac, vc);
     for (int row = row0; row < row1; ++row) {
         if (row + 1 < row1) THN_LA_LOAD(row + 1, kn, qn, an, vn);
-        const float v = SILU ? silu_f(vc) : vc;
+        const float v = SILU ? silu_of<T>(vc) : vc;
         float part = 0.f;
 #pragma unroll
         for (int i = 0; i < PER; ++i) {
             float k = kc[i], q = qc[i];
-            if (SILU) { k = silu_f(k); q = silu_f(q); }
-            const float a = MODE == 0 ? constant : expf(log_logistic(ac[i] + bias[i]) * inv_tau);
+            if (SILU) { k = silu_of<T>(k); q = silu_of<T>(q); }
+            const float a = MODE == 0 ? constant : logistic_power<T>(ac[i] + bias[i], inv_tau);
             s[i] = a * s[i] + k * v;
             part += s[i] * q;
         }

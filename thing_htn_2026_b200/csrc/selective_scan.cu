@@ -20,6 +20,8 @@
 //
 // float32 after the loads: the step size with its softplus, the decay with its exponential, the
 // state, the sums, the gate.  The convolution is summed in float32 and rounded once after silu.
+// With float32 activations the exponentials and logarithms are computed in double and rounded once
+// (exp_of, silu_of, softplus_of in common.cuh).
 #include <math.h>
 
 #include "common.cuh"
@@ -30,8 +32,6 @@ constexpr int kLanes = 8;
 constexpr int kChannels = 16;
 constexpr int kThreads = kLanes * kChannels;
 
-__device__ __forceinline__ float silu_f(float x) { return x / (1.0f + expf(-x)); }
-__device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log1pf(expf(x)); }
 
 template <typename T>
 __global__ void causal_conv_kernel(T* __restrict__ out, const T* __restrict__ proj, int proj_width, int offset,
@@ -56,7 +56,7 @@ __global__ void causal_conv_kernel(T* __restrict__ out, const T* __restrict__ pr
         else v = to_f32<T>(ring[((size_t)slot * taps + (pos - back) % taps) * channels + c]);
         acc += weight[(size_t)c * taps + j] * v;
     }
-    out[e] = from_f32<T>(silu_f(acc));
+    out[e] = from_f32<T>(silu_of<T>(acc));
 }
 
 template <typename T>
@@ -119,19 +119,19 @@ __global__ void __launch_bounds__(kThreads) selective_scan_kernel(
     if (row0 < row1) THN_SCAN_LOAD(row0, bc_, cc, dtc, xc, zc);
     for (int row = row0; row < row1; ++row) {
         if (row + 1 < row1) THN_SCAN_LOAD(row + 1, bn, cn, dtn, xn, zn);
-        const float dt = softplus_f(dtc + bias);
+        const float dt = softplus_of<T>(dtc + bias);
         const float xv = xc;
         const float dx = dt * xv;
         float part = 0.f;
 #pragma unroll
         for (int i = 0; i < PER; ++i) {
-            s[i] = expf(dt * a[i]) * s[i] + dx * bc_[i];
+            s[i] = exp_of<T>(dt * a[i]) * s[i] + dx * bc_[i];
             part += s[i] * cc[i];
         }
 #pragma unroll
         for (int off = kLanes / 2; off > 0; off >>= 1) part += __shfl_xor_sync(0xffffffffu, part, off);
         if (lane == 0 && live)
-            y[(size_t)row * channels + c] = from_f32<T>((part + skip * xv) * silu_f(zc));
+            y[(size_t)row * channels + c] = from_f32<T>((part + skip * xv) * silu_of<T>(zc));
 #pragma unroll
         for (int i = 0; i < PER; ++i) {
             bc_[i] = bn[i];

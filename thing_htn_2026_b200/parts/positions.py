@@ -11,6 +11,9 @@ its tables the same way, engine/engine.py:232-251).
 i + rotary_dim / 2, the default) or "interleaved" (entry 2i with entry 2i + 1).
 ``frequency_precision`` "float64" computes ``inv_freq`` in double precision before it is
 rounded to float32 (one rounding instead of the float32 expression's several).
+``angle_precision`` "float64": the angle ``p * inv_freq`` and its cosine and sine are computed in
+double from the unrounded frequency and rounded once (the float32 product of a position in the
+thousands carries an absolute error of 1e-4 of a turn's radian, which a score sums over a head).
 
 ``scaling`` (a mapping ``factor, original, fast, slow``) stretches the slow pairs for sequences
 longer than ``original`` positions (YaRN).  With ``turn(t) = rotary_dim * ln(original / (2 pi t))
@@ -55,6 +58,11 @@ class Rope:
         else:
             exponent = torch.arange(0, self.rotary_dim, 2, dtype=torch.int64).to(torch.float32) / self.rotary_dim
             self.inv_freq = (1.0 / (self.theta ** exponent)).to(runtime.device)
+        self.exact_angles = spec.params.get("angle_precision") == "float64"
+        if self.exact_angles and spec.params.get("scaling"):
+            raise ValueError("rope: angles in double are built without frequency scaling")
+        self.inv_freq64 = (self.theta ** -(torch.arange(0, self.rotary_dim, 2, dtype=torch.int64).to(torch.float64)
+                                           / self.rotary_dim)).to(runtime.device)
         self.magnitude = 1.0
         scaling = spec.params.get("scaling")
         if scaling:
@@ -83,7 +91,11 @@ class Rope:
         half = self.rotary_dim // 2
         cos = torch.empty((size, half), dtype=torch.float32, device=self.device)
         sin = torch.empty((size, half), dtype=torch.float32, device=self.device)
-        ops.rope_table(cos, sin, self.inv_freq, 0, size)
+        if self.exact_angles:
+            angle = torch.arange(size, dtype=torch.float64, device=self.device)[:, None] * self.inv_freq64[None, :]
+            cos, sin = torch.cos(angle).to(torch.float32).contiguous(), torch.sin(angle).to(torch.float32).contiguous()
+        else:
+            ops.rope_table(cos, sin, self.inv_freq, 0, size)
         if self.magnitude != 1.0:
             cos.mul_(self.magnitude)
             sin.mul_(self.magnitude)
