@@ -236,9 +236,16 @@ def route(ar, h, w, prefix, top):
     return best.indices, best.values / (best.values.sum(-1, keepdim=True) + 1e-20), z
 
 
+MARGINS = None      # a list, while a caller collects per-token routing margins (routing_margin below)
+
+
 def mixture(ar, h, w, prefix, mlp):
     T = h.shape[0]
-    chosen, weight, _ = route(ar, h, w, prefix, mlp["router"]["top"])
+    chosen, weight, z = route(ar, h, w, prefix, mlp["router"]["top"])
+    if MARGINS is not None:
+        top = mlp["router"]["top"]
+        ordered = torch.sort(z, dim=-1, descending=True).values
+        MARGINS.append(ordered[:, top - 1] - ordered[:, top] if top < z.shape[-1] else torch.full((T,), math.inf))
     out = torch.zeros(T, w[prefix + "e0.down"].shape[0], dtype=ar.work)
     for t in range(T):
         for e, c in zip(chosen[t].tolist(), weight[t]):
@@ -300,6 +307,18 @@ def model_forward(folder, tokens, precision=torch.float64, model=None):
 
 def model_logits(folder, tokens, precision=torch.float64, model=None):
     return model_forward(folder, tokens, precision, model)[0]
+
+
+def routing_margin(folder, tokens):
+    """Per token, over all routed layers, the smallest distance between the logit of the last
+    expert chosen and that of the best one left out, in float64: how sure the routing is."""
+    global MARGINS
+    MARGINS = []
+    try:
+        model_forward(folder, tokens, torch.float64)
+        return torch.stack(MARGINS).min(0).values if MARGINS else torch.full((len(tokens),), math.inf)
+    finally:
+        MARGINS = None
 
 
 def greedy(folder, prompt, n_new, precision=torch.float64):
