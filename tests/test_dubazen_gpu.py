@@ -347,7 +347,8 @@ def rope_tables(dim, base, layout="half", n=1024):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("d, dv, n_q, n_kv", [(16, 16, 2, 1), (64, 64, 4, 2), (24, 10, 4, 2), (18, 26, 3, 1), (128, 32, 6, 1)])
+@pytest.mark.parametrize("d, dv, n_q, n_kv", [(16, 16, 2, 1), (64, 64, 4, 2), (24, 10, 4, 2), (18, 26, 3, 1), (128, 32, 6, 1),
+                                              (128, 128, 8, 2), (48, 48, 3, 3), (96, 96, 16, 1)])
 @pytest.mark.parametrize("sink", [None, 2.0, -1.0])
 def test_one_loud_key_among_hundreds_and_the_sink_against_the_closed_form(dtype, d, dv, n_q, n_kv, sink):
     """300 keys of which one is loud, in ten places (the first token, either side of a page border, far
@@ -372,7 +373,12 @@ def test_one_loud_key_among_hundreds_and_the_sink_against_the_closed_form(dtype,
                 rows = kv.rows(count)
                 view = kv.cache.kv_view(0)
                 qq = ops.qk_prepare(proj[at:at + count].contiguous(), None, None, None, 1.0, None, rows, view, n_q, False, True, kv.err)
-                outs.append(ops.attention(qq, rows, view, n_q, scale, None, kv.err, None, exact_weights=True,
+                tiles, size = None, ops.prompt_attention_tile(t, d, 64, n_q, n_kv, dv) if count > 1 else 0
+                if size:        # keys and values of one size that the tensor-core prompt kernel takes
+                    row0, n_rows = ops.row_tiles_of([count], [at], size)
+                    as_dev = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+                    tiles = ops.RowTiles(as_dev(row0), as_dev(n_rows), len(row0), size)
+                outs.append(ops.attention(qq, rows, view, n_q, scale, None, kv.err, tiles, exact_weights=True,
                                           sinks=None if sinks is None else sinks.to(DEV)))
                 kv.done(count)
                 at += count

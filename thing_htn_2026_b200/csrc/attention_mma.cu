@@ -28,8 +28,12 @@ struct KeyWindow {
     int split_weights;
     // What happens to a score between the scale and the softmax (common.cuh); inactive by default.
     ScoreShape shape;
-    __host__ __device__ KeyWindow(int s = 0, int k = 0, int c = 0, int split = 0, ScoreShape sh = ScoreShape{0.f, 0.f, 0})
-        : size(s), keep(s > 0 ? k : 0), chunk(c), split_weights(split), shape(sh) {}
+    // One float32 per query head, or null: the softmax's denominator of head h also holds
+    // exp(sinks[h]), a term without key and value that is not scaled and counts once.
+    const float* sinks;
+    __host__ __device__ KeyWindow(int s = 0, int k = 0, int c = 0, int split = 0, ScoreShape sh = ScoreShape{0.f, 0.f, 0},
+                                  const float* sk = nullptr)
+        : size(s), keep(s > 0 ? k : 0), chunk(c), split_weights(split), shape(sh), sinks(sk) {}
     __host__ __device__ operator int() const { return size; }
     // first position that the query at `pos` sees, kept first positions aside
     __host__ __device__ int first_visible(int pos) const {
@@ -155,6 +159,12 @@ struct RowState {
     __device__ __forceinline__ void init() {
         m[0] = m[1] = -INFINITY;
         l[0] = l[1] = 0.f;
+    }
+    // Row r starts from its head's sink: the sink is the running maximum (log2 domain) and its
+    // term, exp2(sink - sink) = 1, stands in the sum of ONE of the row's four threads (holder).
+    __device__ __forceinline__ void start_from_sink(int r, float sink, bool holder) {
+        m[r] = sink * 1.4426950408889634f;
+        l[r] = holder ? 1.f : 0.f;
     }
 };
 
@@ -284,6 +294,10 @@ __global__ void __launch_bounds__(kPrefillThreads) attention_prefill_kernel(
     RowState st;
     st.init();
     const int g = lane >> 2, tq = lane & 3;
+    if (window.sinks) {
+        st.start_from_sink(0, window.sinks[h], tq == 0);
+        st.start_from_sink(1, window.sinks[h], tq == 0);
+    }
     const int my_pos[2] = {pos0 + warp * 16 + g, pos0 + warp * 16 + g + 8};
     const int my_chunk_start[2] = {window.chunk > 0 ? my_pos[0] / window.chunk * window.chunk : 0,
                                    window.chunk > 0 ? my_pos[1] / window.chunk * window.chunk : 0};
@@ -594,6 +608,14 @@ __global__ void __launch_bounds__(kThreads) attention_decode_kernel(
     RowState st;
     st.init();
     const int tq = lane & 3;
+    if (window.sinks && split == 0 && warp == 0) {
+        // the rows are the heads of the group; the sink enters once, in the first split's first warp
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            const int row = (lane >> 2) + 8 * r;
+            if (row < G) st.start_from_sink(r, window.sinks[kvh * G + row], tq == 0);
+        }
+    }
 
     for (int t = t_begin, stage = 0; t < t_end; ++t, stage = stage + 1 == kStages ? 0 : stage + 1) {
         const int page_now = page_next;
@@ -1582,7 +1604,7 @@ int launch_decode(void* out, float* part_o, float* part_ml, const void* q, const
     // pairs of 1,024 keys on: 4.38 against 4.76 ms per step at batch 24 with 4,096 keys).
     const bool second_pass = (long long)n_pairs > (long long)sm_count() * decode_blocks_per_sm<D, 2>();
     const bool asked_for = (hints & 2) != 0;
-    if (n_splits == 1 && n_pages > 0 && window.keep == 0 && window.chunk == 0 && !window.split_weights && !window.shape.active() && (g_decode_stream == 2 || (g_decode_stream == 1 && (second_pass || asked_for)))) {
+    if (n_splits == 1 && n_pages > 0 && window.keep == 0 && window.chunk == 0 && !window.split_weights && !window.shape.active() && window.sinks == nullptr && (g_decode_stream == 2 || (g_decode_stream == 1 && (second_pass || asked_for)))) {
         const int taken = g_decode_stream_stages >= 6
             ? launch_decode_stream<D, 6, FUSED>(out, q, row_slot, row_pos, kv, n_pages, n_seqs, n_q, scale, window, err,
                                                 stream, fused, hints)
@@ -1671,11 +1693,13 @@ THN_API int thn_attention_prefill_bf16(void* out, const void* q, const int* tile
                                        int n_tiles, const int* row_slot, const int* row_pos, const void* kv_base,
                                        const int* block_table, int bt_stride, int n_kv, int page_size, int head_dim,
                                        int n_q, float scale, int window_size, int keep_first, int chunk, int split_weights,
-                                       float softcap, float temp_coef, int temp_every, int* err, cudaStream_t stream) {
+                                       float softcap, float temp_coef, int temp_every, const float* sinks, int* err,
+                                       cudaStream_t stream) {
     THN_CHECK_ARG(n_tiles >= 0 && n_q > 0 && keep_first >= 0 && chunk >= 0, "attention_prefill: bad sizes");
     THN_CHECK_ARG(chunk == 0 || (window_size <= 0 && keep_first == 0), "attention_prefill: chunks stand instead of a window");
     THN_CHECK_ARG(softcap >= 0.f && temp_every >= 0, "attention_prefill: a score cap and a temperature period are not negative");
-    const KeyWindow window(window_size, keep_first, chunk, split_weights ? 1 : 0, ScoreShape{softcap, temp_coef, temp_every});
+    const KeyWindow window(window_size, keep_first, chunk, split_weights ? 1 : 0, ScoreShape{softcap, temp_coef, temp_every},
+                           sinks);
     THN_UNSUPPORTED_IF(!thn_attention_mma_supported(head_dim, page_size, n_q, n_kv),
                        "attention_prefill: head_dim %d, page %d, heads %d/%d not supported by the tensor-core kernel",
                        head_dim, page_size, n_q, n_kv);
@@ -1755,13 +1779,14 @@ THN_API int thn_attention_decode_bf16(void* out, const void* q, const int* row_s
                                       const void* kv_base, const int* block_table, int bt_stride, int n_kv,
                                       int page_size, int head_dim, int n_seqs, int n_q, int n_splits, float scale,
                                       int window_size, int keep_first, int chunk, int split_weights, float softcap,
-                                      float temp_coef, int temp_every, float* scratch,
+                                      float temp_coef, int temp_every, const float* sinks, float* scratch,
                                       int* counters, long long n_pages, int hints, int* err, cudaStream_t stream) {
     THN_CHECK_ARG(n_seqs >= 0 && n_q > 0 && n_splits >= 1 && n_splits <= 65535 && keep_first >= 0 && chunk >= 0,
                   "attention_decode: bad sizes");
     THN_CHECK_ARG(chunk == 0 || (window_size <= 0 && keep_first == 0), "attention_decode: chunks stand instead of a window");
     THN_CHECK_ARG(softcap >= 0.f && temp_every >= 0, "attention_decode: a score cap and a temperature period are not negative");
-    const KeyWindow window(window_size, keep_first, chunk, split_weights ? 1 : 0, ScoreShape{softcap, temp_coef, temp_every});
+    const KeyWindow window(window_size, keep_first, chunk, split_weights ? 1 : 0, ScoreShape{softcap, temp_coef, temp_every},
+                           sinks);
     THN_CHECK_ARG(counters == nullptr || n_splits <= 32, "attention_decode: at most 32 splits with counters, got %d",
                   n_splits);
     THN_UNSUPPORTED_IF(!thn_attention_mma_supported(head_dim, page_size, n_q, n_kv),
@@ -1876,7 +1901,7 @@ THN_API int thn_attention_decode_bf16_no_alloc(void* out, const void* q, const i
     }
     return thn_attention_decode_bf16(out, q, row_slot, row_pos, kv_base, block_table, bt_stride, n_kv, page_size,
                                      head_dim, n_seqs, n_q, n_splits, scale, window, /*keep_first=*/0, /*chunk=*/0, /*split_weights=*/0,
-                                     /*softcap=*/0.f, /*temp_coef=*/0.f, /*temp_every=*/0, scratch,
+                                     /*softcap=*/0.f, /*temp_coef=*/0.f, /*temp_every=*/0, /*sinks=*/nullptr, scratch,
                                      nullptr, /*n_pages=*/0, /*hints=*/1, err,
                                      stream);
 }

@@ -116,10 +116,10 @@ _SIGNATURES = {
     "thn_attention_fused_supported": [c_int, c_int, c_int, c_int],
     "thn_attention_prefill_bf16": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                                    c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_int,
-                                   c_float, c_float, c_int, c_void_p, c_void_p],
+                                   c_float, c_float, c_int, c_void_p, c_void_p, c_void_p],
     "thn_attention_decode_bf16": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                                   c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_int, c_float, c_float,
-                                  c_int, c_void_p, c_void_p, c_longlong, c_int, c_void_p, c_void_p],
+                                  c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_void_p, c_void_p],
     "thn_attention_decode_blocks_per_sm": [c_int],
     "thn_attention_decode_cluster_splits": [],
     "thn_attention_decode_one_wave_splits": [c_int, c_int, c_int],
@@ -889,20 +889,22 @@ def attention(q: torch.Tensor, rows: StepRows, kv: KVView, n_q: int, scale: floa
     prompts to the latter.  ``shape``: a position-dependent factor on a row's scores and a tanh
     cap (:class:`ScoreShape`), taken by every kernel but the streaming decode kernel.  ``sinks``: a
     term ``exp(sinks[h])`` without key and value in the softmax's denominator of head h; the
-    warp-per-(row, head) kernel takes it."""
+    warp-per-(row, head) kernel and the ``mma.sync`` kernels take it (the tcgen05 prompt kernel and
+    the streaming decode kernel do not, and are not chosen then)."""
     keep_first = int(keep_first or 0) if window else 0
-    if kv.v_dim != kv.head_dim or sinks is not None:
+    if kv.v_dim != kv.head_dim:
         return attention_generic(q, rows, kv, n_q, scale, window, err, keep_first, chunk, exact_weights, shape, sinks)
     if q.dtype == torch.bfloat16 and lib().thn_attention_mma_supported(kv.head_dim, kv.page_size, n_q, kv.n_kv):
         if rows.max_q_len == 1:
             return attention_decode_bf16(q, rows, kv, n_q, scale, window, err, keep_first=keep_first, chunk=chunk,
-                                         split_weights=exact_weights, shape=shape)
+                                         split_weights=exact_weights, shape=shape, sinks=sinks)
         if tiles is not None:
-            if USE_TCGEN05_ATTENTION and lib().thn_attention_tcgen05_supported(kv.head_dim, kv.page_size, n_q, kv.n_kv):
+            if (sinks is None and USE_TCGEN05_ATTENTION
+                    and lib().thn_attention_tcgen05_supported(kv.head_dim, kv.page_size, n_q, kv.n_kv)):
                 return attention_prefill_tcgen05(q, rows, tiles, kv, n_q, scale, window, err, keep_first, chunk, shape)
             return attention_prefill_bf16(q, rows, tiles, kv, n_q, scale, window, err, keep_first, chunk, exact_weights,
-                                          shape)
-    return attention_generic(q, rows, kv, n_q, scale, window, err, keep_first, chunk, exact_weights, shape)
+                                          shape, sinks)
+    return attention_generic(q, rows, kv, n_q, scale, window, err, keep_first, chunk, exact_weights, shape, sinks)
 
 
 def attention_prefill_tcgen05(q: torch.Tensor, rows: StepRows, tiles: RowTiles, kv: KVView, n_q: int, scale: float,
@@ -938,7 +940,7 @@ def _check_tiles(tiles: RowTiles) -> None:
 def attention_prefill_bf16(q: torch.Tensor, rows: StepRows, tiles: RowTiles, kv: KVView, n_q: int, scale: float,
                            window: Optional[int], err: torch.Tensor, keep_first: int = 0,
                            chunk: Optional[int] = None, split_weights: bool = False,
-                           shape: ScoreShape = PLAIN_SCORES) -> torch.Tensor:
+                           shape: ScoreShape = PLAIN_SCORES, sinks: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Tensor-core flash attention for steps with several tokens per sequence.  ``split_weights``:
     the softmax weights multiply the values as two bfloat16 parts (two products), not one."""
     _need(q, "attention q", torch.bfloat16)
@@ -947,7 +949,7 @@ def attention_prefill_bf16(q: torch.Tensor, rows: StepRows, tiles: RowTiles, kv:
     _call("thn_attention_prefill_bf16", _ptr(out), _ptr(q), _ptr(tiles.row0), _ptr(tiles.rows),
           tiles.n, _ptr(rows.row_slot), _ptr(rows.row_pos), _ptr(kv.storage), _ptr(kv.block_table),
           kv.block_table.shape[1], kv.n_kv, kv.page_size, kv.head_dim, n_q, float(scale), int(window or 0),
-          int(keep_first or 0), int(chunk or 0), int(bool(split_weights)), *shape.args(), _ptr(err), _stream())
+          int(keep_first or 0), int(chunk or 0), int(bool(split_weights)), *shape.args(), _ptr(sinks), _ptr(err), _stream())
     return out
 
 
@@ -1011,7 +1013,7 @@ def attention_decode_bf16(q: torch.Tensor, rows: StepRows, kv: KVView, n_q: int,
                           window: Optional[int], err: torch.Tensor, n_splits: Optional[int] = None,
                           scratch: Optional[torch.Tensor] = None, fused_merge: bool = True,
                           keep_first: int = 0, chunk: Optional[int] = None, split_weights: bool = False,
-                          shape: ScoreShape = PLAIN_SCORES) -> torch.Tensor:
+                          shape: ScoreShape = PLAIN_SCORES, sinks: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Split-KV flash decoding: one token per sequence.  Partial results of the splits go
     through float32 scratch memory, which is allocated here unless given."""
     _need(q, "attention q", torch.bfloat16)
@@ -1029,7 +1031,7 @@ def attention_decode_bf16(q: torch.Tensor, rows: StepRows, kv: KVView, n_q: int,
     _call("thn_attention_decode_bf16", _ptr(out), _ptr(q), _ptr(rows.row_slot), _ptr(rows.row_pos),
           _ptr(kv.storage), _ptr(kv.block_table), kv.block_table.shape[1], kv.n_kv, kv.page_size, kv.head_dim,
           n_seqs, n_q, n_splits, float(scale), int(window or 0), int(keep_first or 0), int(chunk or 0),
-          int(bool(split_weights)), *shape.args(), _ptr(scratch), _ptr(counters),
+          int(bool(split_weights)), *shape.args(), _ptr(sinks), _ptr(scratch), _ptr(counters),
           kv.storage.shape[0], decode_hints(rows, kv.n_kv, n_splits, q.device), _ptr(err), _stream())
     return out
 

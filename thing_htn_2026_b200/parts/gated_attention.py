@@ -12,7 +12,9 @@
 The rotation commutes with the division by the root mean square (a rotation keeps a head's length
 and the norm has no gain), so the kernel that normalises first and then turns computes the same.
 One product gives q, k, v and the gate; :func:`ops.qk_prepare` normalises, turns and writes the
-cache in float32 with one rounding; the attention kernel keeps scores and weights in float32;
+cache in float32 with one rounding; the attention kernels keep scores and weights in float32 (the
+tensor-core kernels, which take keys and values of one size from 32 to 128 in bfloat16, multiply
+the values by the weights as two bfloat16 parts);
 :func:`ops.rotate_gate` turns the read-out back and gates it.  A mixer in phases
 (:mod:`.fused`), so that it can share its products with a mixer beside it.
 """
@@ -29,7 +31,7 @@ from ..config.base import PartSpec, ScheduleEntry
 from ..weights.loader import GAIN, MATRIX, TensorSpec
 from .fused import PhasedMixer, cat_bias
 from .registry import part_class, register_part
-from .runtime import Runtime, StepContext
+from .runtime import HostBatch, Runtime, StepContext
 
 
 def _position(runtime: Runtime, spec: Optional[PartSpec]):
@@ -104,14 +106,30 @@ class GatedAttention(PhasedMixer):
     def cache_need(self) -> CacheNeed:
         return KVSpec(self.n_kv, self.head_dim, self.window, 0, None, self.value_dim)
 
+    def _tile(self, page_size: int) -> int:
+        return ops.prompt_attention_tile(self.dtype, self.head_dim, page_size, self.n_q, self.n_kv, self.value_dim)
+
+    def step_inputs(self, batch, out) -> None:
+        """The row tiles of the tensor-core prompt kernel, where the sizes go to it (keys and values
+        of one size that it takes); every attention that wants tiles of one size shares one list."""
+        size = self._tile(batch.page_size) if batch.max_count > 1 else 0
+        if size and f"row_tiles/{size}/row0" not in out:
+            out[f"row_tiles/{size}/row0"], out[f"row_tiles/{size}/rows"] = ops.row_tiles_of(batch.counts, batch.held, size)
+
     def inner(self, x, proj, offset, ctx: StepContext, entry: ScheduleEntry, out, out_offset, scale) -> None:
         kv = ctx.cache.kv_view(entry.cache)
+        tiles = None
+        if ctx.rows.max_q_len > 1:
+            size = self._tile(kv.page_size)
+            row0 = ctx.inputs.get(f"row_tiles/{size}/row0") if size else None
+            if row0 is not None:
+                tiles = ops.RowTiles(row0, ctx.inputs[f"row_tiles/{size}/rows"], row0.shape[0], size)
         rotary = self.position.tables() if self.position is not None else None
         turn = self.value_position.tables() if self.value_position is not None else None
         q = ops.qk_prepare(proj, self.unit_gain, self.unit_gain, "head" if self.eps is not None else None, self.eps or 1.0,
                            rotary, ctx.rows, kv, self.n_q, False, entry.writes_cache, ctx.err, value_rotary=turn,
                            proj_offset=offset)
-        a = ops.attention(q, ctx.rows, kv, self.n_q, self.scale, self.window, ctx.err, None, exact_weights=True,
+        a = ops.attention(q, ctx.rows, kv, self.n_q, self.scale, self.window, ctx.err, tiles, exact_weights=True,
                           sinks=self.sinks)
         if self.gated:
             ops.rotate_gate(a, proj, offset + self.gate_offset, self.n_q, self.value_dim, turn, ctx.rows, ctx.err, scale,
