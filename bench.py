@@ -32,7 +32,11 @@ heads and feed-forward weights, its closest relative here.  ``--design ditilix``
 Ditilix decoder (``ditilix-w2048``, ``ditilix-w4096``: attention over all keys with a score cap and a
 query temperature, every other layer reading the keys of the layer before it, one dense
 feed-forward with a polynomial of norms and seven routed ones) beside a Qwen3 decoder of the same
-width, depth, heads and feed-forward products.  The default run is untouched by all three.
+width, depth, heads and feed-forward products.  ``--design dubazen`` measures the Dubazen decoder
+(``dubazen-w2048``, ``dubazen-w4096``: four copies of the stream joined by hyper-connections, selective
+scans, pairs of softmax attention with sinks and linear attention, gated linear attention, routed
+experts weighted at their output) beside a Bunudra decoder of the same width, depth, heads and
+experts, its closest relative here.  The default run is untouched by all four.
 """
 
 from __future__ import annotations
@@ -1049,6 +1053,235 @@ def ditilix_kernel_table(torch, dit, peak, batch, context):
     return rows
 
 
+DUBAZEN_SIZES = ("dubazen-w2048", "dubazen-w4096")
+
+
+def bunudra_like(dub):
+    """A Bunudra config.json of the same width, depth, vocabulary, head counts and sizes as a Dubazen
+    configuration: a matrix-memory layer for every layer with a recurrent state alone (gated linear
+    attention, selective scan), an attention layer over all keys for every pair of softmax and linear
+    attention, and the same experts (as many, as wide, as many per token, a shared one)."""
+    par = next(l for l in dub["layers"] if l["type"] == "parallel")["mixer"]["left"]
+    layers = []
+    for layer in dub["layers"]:
+        mlp = layer["mlp"]
+        moe = {"kind": "moe", "expert": {"ff": mlp["expert"]["ff"]},
+               "router": {"experts": mlp["router"]["experts"], "top": mlp["router"]["top"], "scale": 1.0},
+               "shared": {"ff": mlp["shared"]["ff"]}}
+        if layer["type"] == "parallel":
+            mixer = {"heads": par["heads"], "kv_heads": par["kv_heads"], "dim": par["dim"], "vdim": par["vdim"],
+                     "scale": par["scale"], "rot": dict(par["rot"])}
+            kind = "attention"
+        else:
+            mixer = {"heads": par["heads"], "dim": 128, "vdim": 128, "gate_cap": 15.0}
+            kind = "mlstm"
+        layers.append({"type": kind, "mixer": mixer, "mlp": moe})
+    return {"architecture": "Bunudra", "vocab": dub["vocab"], "width": dub["width"], "embedding": dub["embedding"],
+            "norm": dub["norm"], "layers": layers}
+
+
+def dubazen_kernel_table(torch, dub, peak, batch, context):
+    """Every kernel of the Dubazen design alone, beside the like kernel of the Bunudra path, cold
+    caches (a buffer larger than L2 is written between timed launches): microseconds, and the
+    fraction of the roofline that the kernel's algorithmic bytes or flops amount to."""
+    from thing_htn_2026_b200 import ops
+    from thing_htn_2026_b200.cache import KVSpec, SequenceCache, StateSpec
+    dev, bf = "cuda:0", torch.bfloat16
+    pair = next(l for l in dub["layers"] if l["type"] == "parallel")["mixer"]
+    left, right = pair["left"], pair["right"]
+    gla = next(l for l in dub["layers"] if l["type"] == "gla")["mixer"]
+    scan = next(l for l in dub["layers"] if l["type"] == "mamba1")["mixer"]
+    mlp = dub["layers"][0]["mlp"]
+    W, T, S = dub["width"], PREFILL_TOKENS, dub["streams"]
+    E, ff, sff, top = mlp["router"]["experts"], mlp["expert"]["ff"], mlp["shared"]["ff"], mlp["router"]["top"]
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    hbm, tensor = peak["hbm_gbs"] * 1e9, peak["bf16_tflops"] * 1e12
+    cores = FP32_CORE_TFLOPS * 1e12
+
+    def timed(fn, reps=7):
+        out = []
+        for _ in range(reps):
+            flush.zero_()
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            fn()
+            end.record()
+            torch.cuda.synchronize()
+            out.append(start.elapsed_time(end) * 1e3)
+        return statistics.median(out[2:])
+
+    rows = {}
+
+    def row(name, fn, nbytes=0, flops=0, flop_peak=None, like=None):
+        us = timed(fn)
+        t_roof = max(nbytes / hbm, flops / (flop_peak or tensor)) * 1e6
+        rows[name] = {"us": round(us, 2), "roofline_us": round(t_roof, 3), "frac": round(t_roof / us, 5), "like": like,
+                      "bound": "hbm" if nbytes / hbm >= flops / (flop_peak or tensor) else "flops"}
+
+    g = torch.Generator(device=dev).manual_seed(0)
+    rnd = lambda *shape: torch.randn(shape, generator=g, device=dev)
+    err = ops.new_error_word(dev)
+    H, G, D, DV = left["heads"], left["kv_heads"], left["dim"], left["vdim"]
+    for n, tag in ((T, "prefill"), (batch, "decode")):
+        # ---- between two sublayers: the streams' write, read and norm, against "layer norm of the branch, add, the sum"
+        X, y16 = rnd(n, S * W), rnd(n, W).to(bf)
+        numbers = ops.StreamNumbers(rnd(S), rnd(S, S), rnd(S))
+        gain1 = torch.ones(1, device=dev)
+        row(f"{tag}: hyper_norm ({S} streams: write, read, norm)",
+            lambda: ops.hyper_norm(X, S, bf, y=y16, written=numbers, read=numbers.read, gain=gain1, eps=1e-6),
+            nbytes=n * W * (8 * S + 2 + 2), like=f"{tag}: residual_norm (layer norm of the branch, add, the sum as it is)")
+        h32 = rnd(n, W)
+        layer = ops.Gain(1 + rnd(W) * 0.1, 0.0, 1e-6, rnd(W) * 0.1, "layer")
+        row(f"{tag}: residual_norm (layer norm of the branch, add, the sum as it is)",
+            lambda: ops.residual_norm(h32, y16, layer, ops.STREAM_AS_IS, bf), nbytes=n * W * (4 + 4 + 2 + 2))
+        # ---- routing and the experts' activation
+        z = rnd(n, E + 1)
+        routing = ops.moe_route(z, E, 1, 1, top, 1.0, renormalise=1e-20)
+        row(f"{tag}: moe_route (softmax, renormalised)", lambda: ops.moe_route(z, E, 1, 1, top, 1.0, renormalise=1e-20),
+            nbytes=n * ((E + 1) * 4 + E * 4 + top * 8), like=f"{tag}: moe_route (softmax, groups)")
+        row(f"{tag}: moe_route (softmax, groups)",
+            lambda: ops.moe_route(z, E, 4 if E % 4 == 0 else 1, 2 if E % 4 == 0 else 1, top, 2.0),
+            nbytes=n * ((E + 1) * 4 + E * 4 + top * 8))
+        gu, u = rnd(n, 2 * (E * ff + sff)).to(bf), rnd(n, E * ff + sff).to(bf)
+        row(f"{tag}: routed_clamped_glu (weight on the output)",
+            lambda: ops.routed_clamped_glu(gu, routing, ff, sff, mlp["expert"]["limit"], mlp["shared"]["limit"], 1.702,
+                                           weight_at="output"),
+            nbytes=n * (2 * (top * ff + sff) * 2 + (E * ff + sff) * 2), like=f"{tag}: routed_gelu")
+        row(f"{tag}: routed_gelu", lambda: ops.routed_gelu(u, routing, ff, sff, z, E),
+            nbytes=n * ((top * ff + sff) * 2 + (E * ff + sff) * 2))
+        # ---- the read-outs on their way to the shared output product
+        a16, g16 = rnd(n, H * DV).to(bf), rnd(n, H * DV + 64).to(bf)
+        positions = ops.StepRows(None, torch.arange(n, dtype=torch.int32, device=dev) + (0 if n == T else context), None, None,
+                                 n, 1, 1)
+        turn = ops.RotaryTables(torch.ones(8192, DV // 2, device=dev), torch.zeros(8192, DV // 2, device=dev), DV, "half")
+        joint = torch.empty(n, H * DV + right["heads"] * right["vdim"], dtype=bf, device=dev)
+        row(f"{tag}: rotate_gate (turned back, gated, scaled, into its columns)",
+            lambda: ops.rotate_gate(a16, g16, 64, H, DV, turn, positions, err, 0.6, joint, 0), nbytes=n * H * DV * 6,
+            like=f"{tag}: logistic_gate")
+        row(f"{tag}: logistic_gate", lambda: ops.logistic_gate(a16, g16, 64), nbytes=n * H * DV * 6)
+        Hr, Er = right["heads"], right["vdim"]
+        o32, gate_r = rnd(n, Hr, Er), rnd(n, Hr * Er).to(bf)
+        w_all = 1 + rnd(Hr * Er) * 0.1
+        row(f"{tag}: gated_head_norm (one norm over all heads, logistic, scaled, into its columns)",
+            lambda: ops.gated_head_norm(o32, gate_r, 0, w_all, 1e-6, 1, Hr * Er, bf, "logistic", 0.9, joint, H * DV),
+            nbytes=n * Hr * Er * 8, like=f"{tag}: gated_head_norm (per head, logistic, a gain over all heads)")
+        row(f"{tag}: gated_head_norm (per head, logistic, a gain over all heads)",
+            lambda: ops.gated_head_norm(o32, gate_r, 0, w_all, 1e-6, Hr, Er, bf, gate_kind="logistic"), nbytes=n * Hr * Er * 8)
+
+    # ---- attention over a paged cache: one sequence of T tokens, then `batch` sequences at `context` keys
+    tables = ops.RotaryTables(torch.ones(8192, left["rot"]["dims"] // 2, device=dev),
+                              torch.zeros(8192, left["rot"]["dims"] // 2, device=dev), left["rot"]["dims"], "half")
+    turn = ops.RotaryTables(torch.ones(8192, DV // 2, device=dev), torch.zeros(8192, DV // 2, device=dev), DV, "half")
+    ones, gains = torch.ones(D, device=dev), 1 + rnd(D) * 0.1
+    sinks = rnd(H)
+    width = (H + G) * D + G * DV
+
+    def attention_rows(tags, prepare_of, sink, likes):
+        cache = SequenceCache([KVSpec(G, D, None, 0, None, DV)], max_tokens=(batch * (context + 64) + T + 64), dtype=bf,
+                              device=dev, max_slots=batch + 2)
+        slots = cache.open(batch + 1)
+        prepare = prepare_of(cache)
+
+        def step_of(slot_list, counts):
+            cache.prepare(slot_list, counts)
+            cu = [0]
+            for c in counts:
+                cu.append(cu[-1] + c)
+            cu_dev = torch.tensor(cu, dtype=torch.int32, device=dev)
+            slots_dev = torch.tensor(slot_list, dtype=torch.int32, device=dev)
+            rows_ = ops.step_rows(cu_dev, slots_dev, cache.seq_lens, cu[-1], max(counts),
+                                  max_context=max(cache.length(s) + c for s, c in zip(slot_list, counts)),
+                                  lengths_differ=False)
+            return rows_, cu_dev, slots_dev
+
+        rows_, cu_dev, slots_dev = step_of([slots[0]], [T])
+        proj = rnd(T, width).to(bf)
+        size = ops.prompt_attention_tile(bf, D, cache.page_size, H, G, DV)
+        tiles = None
+        if size:
+            r0, rn = ops.row_tiles_of([T], [0], size)
+            tiles = ops.RowTiles(torch.tensor(r0, dtype=torch.int32, device=dev), torch.tensor(rn, dtype=torch.int32, device=dev),
+                                 len(r0), size)
+        row(f"prefill: {tags[0]}", lambda: prepare(proj, rows_), nbytes=T * width * 4, like=likes[0])
+        q = prepare(proj, rows_)
+        row(f"prefill: {tags[1]}",
+            lambda: ops.attention(q, rows_, cache.kv_view(0), H, left["scale"], None, err, tiles, exact_weights=True, sinks=sink),
+            flops=2.0 * H * (D + DV) * T * (T + 1) / 2, nbytes=T * H * (D + DV) * 2, like=likes[1])
+        others = slots[1:]
+        rows_, cu_dev, slots_dev = step_of(others, [context] * batch)
+        prepare(rnd(batch * context, width).to(bf), rows_)
+        ops.advance(cache.seq_lens, slots_dev, cu_dev)
+        cache.commit(others, [context] * batch)
+        rows_, cu_dev, slots_dev = step_of(others, [1] * batch)
+        proj1 = rnd(batch, width).to(bf)
+        row(f"decode: {tags[0]}", lambda: prepare(proj1, rows_), nbytes=batch * width * 4, like=likes[2])
+        q1 = prepare(proj1, rows_)
+        row(f"decode: {tags[1]}",
+            lambda: ops.attention(q1, rows_, cache.kv_view(0), H, left["scale"], None, err, None, exact_weights=True, sinks=sink),
+            nbytes=batch * G * (context + 1) * (D + DV) * 2, like=likes[3])
+
+    like_tags = ("qk_prepare (head norm, rotation)", "attention (all keys, float32 weights)")
+    attention_rows(like_tags, lambda cache: (lambda proj, rows_: ops.qk_prepare(proj, gains, gains, "head", 1e-6, tables, rows_,
+                                                                                cache.kv_view(0), H, False, True, err)),
+                   None, (None,) * 4)
+    attention_rows(("qk_prepare (head norm, rotation, values turned)", "attention (all keys, float32 weights, sinks)"),
+                   lambda cache: (lambda proj, rows_: ops.qk_prepare(proj, ones, ones, "head", 1e-6, tables, rows_,
+                                                                     cache.kv_view(0), H, False, True, err, value_rotary=turn)),
+                   sinks, tuple(f"{t}: {x}" for t in ("prefill", "decode") for x in like_tags))
+
+    # ---- the recurrences: one sequence of T tokens, `batch` sequences of one token
+    Hg, dk, dv = gla["heads"], gla["dim"], gla["vdim"]
+    inner, N, taps = scan["inner"], scan["state"], scan["conv"]
+    blocks = ops.mlstm_column_blocks(dv)
+    n_slots = batch + 1
+    cache = SequenceCache([(StateSpec((Hg, dv, dk)), StateSpec((Hg, blocks, dk + 1))), StateSpec((Hg, dv, dk)),
+                           (StateSpec((inner, N)), StateSpec((taps, inner), bf))],
+                          max_tokens=n_slots * 64, dtype=bf, device=dev, max_slots=n_slots + 1)
+    slots = cache.open(n_slots)
+    bias_i, bias_f = rnd(Hg), rnd(Hg) + 3.0
+    decay = torch.tensor([1.0 - 2.0 ** -(3 + 8 * h / max(1, Hg - 1)) for h in range(Hg)], device=dev)
+    conv_w, conv_b = rnd(inner, taps) * 0.5, rnd(inner) * 0.1
+    a_neg, d_skip, dt_bias = -torch.exp(rnd(inner, N) * 0.5), 1 + rnd(inner) * 0.1, rnd(inner) * 0.1
+    gate_bias = rnd(Hg * dk) + 3.0
+    for n, pick, tag in ((T, slice(0, 1), "prefill"), (1, slice(1, None), "decode")):
+        who = slots[pick]
+        cu = torch.arange(len(who) + 1, dtype=torch.int32, device=dev) * n
+        tokens = n * len(who)
+        rows_ = ops.step_rows(cu, torch.tensor(who, dtype=torch.int32, device=dev), cache.seq_lens, tokens, n)
+        proj = (rnd(tokens, Hg * (2 * dk + 2 * dv)) * 0.5).to(bf)
+        pre = rnd(tokens, 2 * Hg)
+        zgate = rnd(tokens, Hg * dk)
+        state_bytes = len(who) * Hg * dk * dv * 4 * 2
+        io_bytes = tokens * (Hg * (2 * dk + dv) * 2 + Hg * dv * 4)
+        like = f"{tag}: mlstm (gates, recurrence)"
+        row(like, lambda: ops.mlstm(proj, pre, bias_i, bias_f, 15.0, cache.state_view(0, 0), cache.state_view(0, 1), rows_, Hg, dk,
+                                    dv, dk ** -0.5),
+            nbytes=state_bytes + io_bytes, flops=6.0 * tokens * Hg * dk * dv, flop_peak=cores)
+        row(f"{tag}: linear_attention (a constant decay per head, silu'd inputs)",
+            lambda: ops.linear_attention(proj, (0, Hg * dk, 2 * Hg * dk), cache.state_view(1), rows_, Hg, dk, dv, decay=decay,
+                                         silu_inputs=True),
+            nbytes=state_bytes + io_bytes, flops=6.0 * tokens * Hg * dk * dv, flop_peak=cores, like=like)
+        row(f"{tag}: linear_attention (a gated decay per key channel)",
+            lambda: ops.linear_attention(proj, (0, Hg * dk, 2 * Hg * dk), cache.state_view(1), rows_, Hg, dk, dv, gate=zgate,
+                                         gate_bias=gate_bias, tau=16.0, q_scale=dk ** -0.5),
+            nbytes=state_bytes + io_bytes + tokens * Hg * dk * 4, flops=6.0 * tokens * Hg * dk * dv, flop_peak=cores, like=like)
+        xz = rnd(tokens, 2 * inner).to(bf)
+        row(f"{tag}: causal_conv (taps, bias, silu) and its ring",
+            lambda: (ops.causal_conv(xz, 0, inner, conv_w, conv_b, cache.state_view(2, 1), rows_, cache.seq_lens),
+                     ops.conv_ring_update(cache.state_view(2, 1), xz, 0, rows_, cache.seq_lens)),
+            nbytes=tokens * inner * 4 + len(who) * taps * inner * 4)
+        xc, dt_pre, bc = rnd(tokens, inner).to(bf), rnd(tokens, inner), rnd(tokens, 2 * N).to(bf)
+        row(f"{tag}: selective_scan",
+            lambda: ops.selective_scan(xc, dt_pre, dt_bias, bc, a_neg, d_skip, xz, inner, cache.state_view(2, 0), rows_),
+            nbytes=len(who) * inner * N * 8 + tokens * (inner * (2 + 4 + 2 + 2) + 4 * N), flops=6.0 * tokens * inner * N,
+            flop_peak=cores, like=like)
+    ops.raise_on_device_error(err, "kernel table")
+    for name, r in rows.items():
+        if r["like"] in rows and r["frac"] > 0:
+            r["times_farther_than_like"] = round(rows[r["like"]]["frac"] / r["frac"], 2)
+    return rows
+
+
 def run_design(args):
     import torch
     from thing_htn_2026_b200 import Engine, ops
@@ -1061,7 +1294,7 @@ def run_design(args):
     sampler.start()
     ops.launch_count = 0
     design = args.design
-    design_sizes = {"lanilix": DESIGN_SIZES, "bunudra": BUNUDRA_SIZES, "ditilix": DITILIX_SIZES}[design]
+    design_sizes = {"lanilix": DESIGN_SIZES, "bunudra": BUNUDRA_SIZES, "ditilix": DITILIX_SIZES, "dubazen": DUBAZEN_SIZES}[design]
     for name in design_sizes:
         lan = named_config_json(name)
         if args.layers:
@@ -1071,7 +1304,8 @@ def run_design(args):
         entry = {"layers": [l["type"] for l in lan["layers"]], "width": lan["width"]}
         beside = {"lanilix": lambda: ("qwen3_same_size", qwen3_like(lan)),
                   "bunudra": lambda: ("lanilix_same_size", lanilix_like(lan)),
-                  "ditilix": lambda: ("qwen3_same_size", qwen3_like_ditilix(lan))}[design]()
+                  "ditilix": lambda: ("qwen3_same_size", qwen3_like_ditilix(lan)),
+                  "dubazen": lambda: ("bunudra_same_size", bunudra_like(lan))}[design]()
         for label, data in ((design, lan), beside):
             engine = Engine.from_config(config_from_dict(data), seed=0, dtype="bfloat16", max_tokens=max_tokens,
                                         max_batch=args.batch)
@@ -1079,7 +1313,8 @@ def run_design(args):
                                          args.prompt_len, steps, warmup)
             del engine
             torch.cuda.empty_cache()
-        table = {"lanilix": kernel_table, "bunudra": bunudra_kernel_table, "ditilix": ditilix_kernel_table}[design]
+        table = {"lanilix": kernel_table, "bunudra": bunudra_kernel_table, "ditilix": ditilix_kernel_table,
+                 "dubazen": dubazen_kernel_table}[design]
         entry["kernels"] = table(torch, lan, peak, args.batch, args.prompt_len)
         sizes[name] = entry
     clocks = sampler.stop()
@@ -1294,7 +1529,7 @@ def main():
                              "(for ncu --profile-from-start off)")
     parser.add_argument("--workload", choices=sorted(LARGE_WORKLOADS), default=None,
                         help="one of the two larger workloads instead of the default run")
-    parser.add_argument("--design", choices=["lanilix", "bunudra", "ditilix"], default=None,
+    parser.add_argument("--design", choices=["lanilix", "bunudra", "ditilix", "dubazen"], default=None,
                         help="another design beside its closest relative at the same sizes (Lanilix beside Qwen3, "
                              "Bunudra beside Lanilix, Ditilix beside Qwen3), model by model and kernel by kernel, "
                              "instead of the default run")

@@ -113,3 +113,23 @@ def test_a_ditilix_model_written_and_run_from_the_command_line(tmp_path):
     lines = [json.loads(line) for line in run_cli("bench", "--random-config", "ditilix-tiny", "--shapes", "2x16x8",
                                                   "--repeats", "1")]
     assert lines[0]["shape"] == "2x16x8" and lines[0]["tok_per_s"] > 0
+
+
+def test_a_dubazen_model_written_and_run_from_the_command_line(tmp_path):
+    """The same for the fifth architecture, with two copies of the stream, a scan, a pair of mixers and
+    a layer without a feed-forward: a named configuration written as a folder, read back by
+    ``generate``, the entry point's tokens, ``bench``, and the replay program on the folder."""
+    from thing_htn_2026_b200 import Engine, cli
+    folder = str(tmp_path / "dubazen")
+    assert run_cli("random-model", "--random-config", "dubazen-tiny", "--seed", "4", "--out", folder, "--dtype",
+                   "bfloat16") == [folder]
+    with open(os.path.join(folder, "config.json")) as handle:
+        assert json.load(handle)["architecture"] == "Dubazen"
+    printed = [json.loads(line) for line in run_cli("generate", "--model", folder, "--prompt-lens", "3,70,21", "--seed", "5",
+                                                    "--max-new-tokens", "9", "--dtype", "float32")]
+    engine = Engine(folder, dtype="float32")
+    steps = list(engine.generate(cli.make_prompts_of([3, 70, 21], engine.model.vocab_size, 5), 9))
+    assert [p["tokens"] for p in printed] == [[step[j] for step in steps] for j in range(3)]
+    lines = [json.loads(line) for line in run_cli("bench", "--random-config", "dubazen-tiny", "--shapes", "2x16x8",
+                                                  "--repeats", "1")]
+    assert lines[0]["shape"] == "2x16x8" and lines[0]["tok_per_s"] > 0

@@ -230,6 +230,63 @@ __global__ void rotate_gate_kernel(T* __restrict__ out, long long out_stride, co
     out[m * out_stride + c] = from_f32<T>(v / (1.0f + expf(-z)) * scale);
 }
 
+// The same for bfloat16 rows in the layout of halves, eight consecutive entries per thread (16-byte
+// accesses): entries d .. d + 7 and their eight partners lie in one half each when half the
+// rotated size is a multiple of eight.
+__global__ void rotate_gate_bf16_vec_kernel(__nv_bfloat16* __restrict__ out, long long out_stride,
+                                            const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ g,
+                                            long long g_stride, const float* __restrict__ cos_tab,
+                                            const float* __restrict__ sin_tab, int table_len, int rotary_dim,
+                                            const int* __restrict__ row_pos, int n_heads, int size, float scale,
+                                            int* __restrict__ err) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int width = n_heads * size;
+    const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+    if (c >= width) return;
+    const long long m = blockIdx.y;
+    const int d = c % size, half = rotary_dim / 2;
+    const uint4 ra = *reinterpret_cast<const uint4*>(a + m * width + c);
+    const uint4 rg = *reinterpret_cast<const uint4*>(g + m * g_stride + c);
+    const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&ra);
+    const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&rg);
+    float v[8];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const float2 x = __bfloat1622float2(a2[j]);
+        v[2 * j] = x.x;
+        v[2 * j + 1] = x.y;
+    }
+    if (cos_tab != nullptr && d < rotary_dim) {
+        const int pos = row_pos[m];
+        if (pos >= table_len) {
+            if (err) atomicOr(err, THN_ERR_POSITION_RANGE);
+            return;
+        }
+        const bool first = d < half;
+        const int i = first ? d : d - half;
+        const uint4 rp = *reinterpret_cast<const uint4*>(a + m * width + (first ? c + half : c - half));
+        const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&rp);
+        const float* co = cos_tab + (size_t)pos * half + i;
+        const float* sn = sin_tab + (size_t)pos * half + i;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float2 other = __bfloat1622float2(p2[j]);
+            v[2 * j] = first ? v[2 * j] * co[2 * j] + other.x * sn[2 * j] : v[2 * j] * co[2 * j] - other.x * sn[2 * j];
+            v[2 * j + 1] = first ? v[2 * j + 1] * co[2 * j + 1] + other.y * sn[2 * j + 1]
+                                 : v[2 * j + 1] * co[2 * j + 1] - other.y * sn[2 * j + 1];
+        }
+    }
+    uint4 packed;
+    __nv_bfloat162* ob = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const float2 z = __bfloat1622float2(g2[j]);
+        ob[j] = __floats2bfloat162_rn(v[2 * j] / (1.0f + expf(-z.x)) * scale, v[2 * j + 1] / (1.0f + expf(-z.y)) * scale);
+    }
+    *reinterpret_cast<uint4*>(out + m * out_stride + c) = packed;
+}
+
 THN_API int thn_rotate_gate(void* out, long long out_stride, const void* a, const void* g, long long g_stride,
                             const float* cos_tab, const float* sin_tab, int table_len, int rotary_dim, int interleaved,
                             const int* row_pos, int n_rows, int n_heads, int size, float scale, int dtype, int* err,
@@ -242,6 +299,16 @@ THN_API int thn_rotate_gate(void* out, long long out_stride, const void* a, cons
     const long long n = (long long)n_rows * n_heads * size;
     if (n == 0) return THN_OK;
     const unsigned blocks = (unsigned)((n + 255) / 256);
+    const bool turns = cos_tab != nullptr && rotary_dim > 0;
+    if (dtype == THN_BF16 && size % 8 == 0 && out_stride % 8 == 0 && g_stride % 8 == 0 && n_rows <= 65535 &&
+        (!turns || (!interleaved && (rotary_dim / 2) % 8 == 0)) &&
+        ((((uintptr_t)out) | ((uintptr_t)a) | ((uintptr_t)g)) & 15) == 0) {
+        const int width = n_heads * size;
+        thn_launch(rotate_gate_bf16_vec_kernel, dim3((width / 8 + 127) / 128, n_rows), 128, 0, stream, (__nv_bfloat16*)out,
+                   out_stride, (const __nv_bfloat16*)a, (const __nv_bfloat16*)g, g_stride, cos_tab, sin_tab, table_len,
+                   turns ? rotary_dim : 0, row_pos, n_heads, size, scale, err);
+        return thn_launch_status("rotate_gate");
+    }
     if (dtype == THN_F32)
         thn_launch(rotate_gate_kernel<float>, blocks, 256, 0, stream, (float*)out, out_stride, (const float*)a,
                    (const float*)g, g_stride, cos_tab, sin_tab, table_len, rotary_dim, interleaved, row_pos, n, n_heads, size,

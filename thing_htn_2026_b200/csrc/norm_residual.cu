@@ -290,6 +290,50 @@ __global__ void gated_head_norm_kernel(T* __restrict__ out, const float* __restr
             from_f32<T>(src[i] * rstd * wh[i] * (gate_kind ? logistic : z * logistic) * scale);
     }
 }
+// One "head" that is a whole long row (one norm over all heads together): a block of 256 threads
+// per row instead of a warp, four consecutive entries per thread where the sizes allow.  The
+// order of additions depends on the size only.
+template <typename T>
+__global__ void __launch_bounds__(256) gated_row_norm_kernel(T* __restrict__ out, const float* __restrict__ o,
+                                                             const T* __restrict__ gate, long long gate_stride,
+                                                             const float* __restrict__ w, float eps, int size,
+                                                             int gate_kind, long long out_stride, float scale) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ float scratch[33];
+    const long long m = blockIdx.x;
+    const float* src = o + m * size;
+    const T* g = gate + m * gate_stride;
+    T* dst = out + m * out_stride;
+    const bool vec = size % 4 == 0 && (((uintptr_t)src | (uintptr_t)w) & 15) == 0;
+    float ss = 0.f;
+    if (vec) {
+        for (int i = threadIdx.x * 4; i < size; i += 1024) {
+            const float4 v = *reinterpret_cast<const float4*>(src + i);
+            ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        }
+    } else {
+        for (int i = threadIdx.x; i < size; i += 256) ss += src[i] * src[i];
+    }
+    const float rstd = 1.0f / sqrtf(block_sum(ss, scratch) / (float)size + eps);
+    auto gated = [&](float v, float gain, float z) {
+        const float logistic = 1.0f / (1.0f + expf(-z));
+        return v * rstd * gain * (gate_kind ? logistic : z * logistic) * scale;
+    };
+    if (vec) {
+        for (int i = threadIdx.x * 4; i < size; i += 1024) {
+            const float4 v = *reinterpret_cast<const float4*>(src + i);
+            const float4 gw = *reinterpret_cast<const float4*>(w + i);
+            dst[i] = from_f32<T>(gated(v.x, gw.x, to_f32<T>(g[i])));
+            dst[i + 1] = from_f32<T>(gated(v.y, gw.y, to_f32<T>(g[i + 1])));
+            dst[i + 2] = from_f32<T>(gated(v.z, gw.z, to_f32<T>(g[i + 2])));
+            dst[i + 3] = from_f32<T>(gated(v.w, gw.w, to_f32<T>(g[i + 3])));
+        }
+    } else {
+        for (int i = threadIdx.x; i < size; i += 256) dst[i] = from_f32<T>(gated(src[i], w[i], to_f32<T>(g[i])));
+    }
+}
+
 // The same with four consecutive entries per lane (16-byte loads of the read-out, 8-byte loads
 // of the gate and stores), for sizes that are multiples of four and suitably aligned rows.
 __global__ void gated_head_norm_bf16_vec_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict__ o,
@@ -380,6 +424,15 @@ THN_API int thn_gated_head_norm(void* out, const float* o, const void* gate, lon
         ((((uintptr_t)o | (uintptr_t)w) & 15) | (((uintptr_t)gate | (uintptr_t)out) & 7)) == 0) {
         thn_launch(gated_head_norm_bf16_vec_kernel, blocks, warps * 32, 0, stream, (__nv_bfloat16*)out, o,
                    (const __nv_bfloat16*)gate, gate_stride, w, eps, units, n_heads, size);
+        return thn_launch_status("gated_head_norm");
+    }
+    if (n_heads == 1 && size >= 512 && (dtype == THN_F32 || dtype == THN_BF16)) {
+        if (dtype == THN_F32)
+            thn_launch(gated_row_norm_kernel<float>, rows, 256, 0, stream, (float*)out, o, (const float*)gate, gate_stride, w, eps,
+                       size, gate_kind, out_stride, scale);
+        else
+            thn_launch(gated_row_norm_kernel<__nv_bfloat16>, rows, 256, 0, stream, (__nv_bfloat16*)out, o,
+                       (const __nv_bfloat16*)gate, gate_stride, w, eps, size, gate_kind, out_stride, scale);
         return thn_launch_status("gated_head_norm");
     }
     if (dtype == THN_F32)

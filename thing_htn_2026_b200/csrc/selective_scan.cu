@@ -14,9 +14,9 @@
 //                 rows or, before the step's first row, from the ring: the last `taps` raw inputs
 //                 of the sequence, position p at p mod taps.
 //   conv_ring_update   after every reader of the ring has ended: the step's last raw inputs go in.
-//   selective_scan     a channel's state is held by 8 lanes (entry n by lane n mod 8); one block
-//                 per (sequence, 16 channels) walks the sequence's tokens of the step in order,
-//                 the next token's operands loaded while the current one is worked on.
+//   selective_scan     a channel's state is held by 4 lanes (8 for states above 32; entry n by lane
+//                 n mod lanes); one block per (sequence, 64 or 32 channels) walks the sequence's tokens of the step in order;
+//                 the tokens come through shared memory, sixteen at a time in two buffers.
 //
 // float32 after the loads: the step size with its softplus, the decay with its exponential, the
 // state, the sums, the gate.  The convolution is summed in float32 and rounded once after silu.
@@ -28,9 +28,6 @@
 
 namespace {
 
-constexpr int kLanes = 8;
-constexpr int kChannels = 16;
-constexpr int kThreads = kLanes * kChannels;
 
 
 template <typename T>
@@ -77,69 +74,153 @@ __global__ void conv_ring_update_kernel(T* __restrict__ ring, const T* __restric
     }
 }
 
-template <typename T, int PER>
-__global__ void __launch_bounds__(kThreads) selective_scan_kernel(
+// LANES lanes hold a channel's state, PER entries each; NP = LANES * PER: the padded state size of a
+// staged token's B and C.  A block of 256 threads takes 256 / LANES channels: 64 with four lanes
+// (states up to 32), so that a token's step sizes, inputs and gates are runs of 128 to 256 bytes.
+// A staged token is [B | C | dt of the block's channels | x | silu(z)]; FETCH values per thread
+// and stage.  Every thread fetches its part of the next stage into registers, the block works
+// through the current one, then the fetched values are transformed once per block (the step size
+// with its bias and softplus, the gate with its silu) and stored for all lanes to read.
+constexpr int kStage = 16;
+constexpr int kScanThreads = 256;
+
+// A value as it was loaded, untouched: turning it into a float is a use, and a use makes the thread
+// wait for the load.  The stage's loads are all issued first and turned into floats when they are stored.
+template <typename T> __device__ __forceinline__ uint32_t raw_load(const T* p);
+template <> __device__ __forceinline__ uint32_t raw_load<float>(const float* p) { return *reinterpret_cast<const uint32_t*>(p); }
+template <> __device__ __forceinline__ uint32_t raw_load<__nv_bfloat16>(const __nv_bfloat16* p) {
+    return *reinterpret_cast<const unsigned short*>(p);
+}
+template <typename T> __device__ __forceinline__ float from_raw(uint32_t bits);
+template <> __device__ __forceinline__ float from_raw<float>(uint32_t bits) { return __uint_as_float(bits); }
+template <> __device__ __forceinline__ float from_raw<__nv_bfloat16>(uint32_t bits) { return __uint_as_float(bits << 16); }
+
+template <typename T, int LANES, int PER, int FETCH>
+__global__ void __launch_bounds__(kScanThreads) selective_scan_kernel(
     T* __restrict__ y, float* __restrict__ state, const T* __restrict__ x, const float* __restrict__ dt_pre,
     const float* __restrict__ dt_bias, const T* __restrict__ bc, int bc_width, const float* __restrict__ A,
     const float* __restrict__ D, const T* __restrict__ z, int z_stride, const int* __restrict__ cu_seqlens,
     const int* __restrict__ slots, int channels, int n_state) {
     pdl_launch_dependents();
     pdl_wait();
+    constexpr int kLanes = LANES, kChannels = kScanThreads / LANES, kThreads = kScanThreads;
+    constexpr int NP = kLanes * PER, ROW = 2 * NP + 3 * kChannels;
+    __shared__ float stage_mem[2 * kStage * ROW];
+    __shared__ float bias_mem[kChannels];
     const int seq = blockIdx.y;
-    const int channel = blockIdx.x * kChannels + threadIdx.x / kLanes;
-    const int lane = threadIdx.x % kLanes;
+    const int c0 = blockIdx.x * kChannels;
+    const int group = threadIdx.x / kLanes, lane = threadIdx.x % kLanes;
+    const int channel = c0 + group;
     const bool live = channel < channels;
     const int c = live ? channel : channels - 1;
     const int row0 = cu_seqlens[seq], row1 = cu_seqlens[seq + 1];
     const int slot = slots[seq];
     float* S = state + ((size_t)slot * channels + c) * n_state;
 
-    float s[PER], a[PER], bc_[PER], cc[PER], bn[PER], cn[PER];     // B and C of the current and of the next token
-    float dtc = 0.f, xc = 0.f, zc = 0.f, dtn = 0.f, xn = 0.f, zn = 0.f;
+    float s[PER], a[PER];
 #pragma unroll
     for (int i = 0; i < PER; ++i) {
         const int n = lane + kLanes * i;
         s[i] = n < n_state ? S[n] : 0.f;
         a[i] = n < n_state ? A[(size_t)c * n_state + n] : 0.f;
     }
-    const float bias = dt_bias[c], skip = D[c];
+    const float skip = D[c];
+    if (threadIdx.x < kChannels) bias_mem[threadIdx.x] = dt_bias[min(c0 + (int)threadIdx.x, channels - 1)];
 
-#define THN_SCAN_LOAD(ROW, B_, C_, DT_, X_, Z_)                                                        \
-    do {                                                                                               \
-        _Pragma("unroll") for (int i = 0; i < PER; ++i) {                                              \
-            const int n = lane + kLanes * i;                                                           \
-            B_[i] = n < n_state ? to_f32<T>(bc[(size_t)(ROW) * bc_width + n]) : 0.f;                   \
-            C_[i] = n < n_state ? to_f32<T>(bc[(size_t)(ROW) * bc_width + n_state + n]) : 0.f;         \
-        }                                                                                              \
-        DT_ = dt_pre[(size_t)(ROW) * channels + c];                                                    \
-        X_ = to_f32<T>(x[(size_t)(ROW) * channels + c]);                                               \
-        Z_ = to_f32<T>(z[(size_t)(ROW) * z_stride + c]);                                               \
-    } while (0)
+    uint32_t fetched[FETCH];
+    auto fetch = [&](int first_row) {
+#pragma unroll
+        for (int j = 0; j < FETCH; ++j) {
+            const int e = threadIdx.x + j * kThreads;
+            const int t = e / ROW, k = e - t * ROW;
+            const int row = first_row + t;
+            uint32_t v = 0;
+            if (row < row1) {
+                if (k < 2 * NP) {
+                    const int which = k / NP, n = k - which * NP;
+                    if (n < n_state) v = raw_load<T>(bc + (size_t)row * bc_width + which * n_state + n);
+                } else {
+                    const int which = (k - 2 * NP) / kChannels, ch = min(c0 + (k - 2 * NP) % kChannels, channels - 1);
+                    if (which == 0) v = raw_load<float>(dt_pre + (size_t)row * channels + ch);
+                    else if (which == 1) v = raw_load<T>(x + (size_t)row * channels + ch);
+                    else v = raw_load<T>(z + (size_t)row * z_stride + ch);
+                }
+            }
+            fetched[j] = v;
+        }
+    };
+    auto publish = [&](int buf, int n) {
+        float* dst = stage_mem + buf * kStage * ROW;
+#pragma unroll
+        for (int j = 0; j < FETCH; ++j) {
+            const int e = threadIdx.x + j * kThreads;
+            if (e >= n * ROW) continue;          // what lies beyond the step's tokens is neither transformed nor read
+            const int k = e % ROW;
+            float v;
+            if (k >= 2 * NP + 2 * kChannels) v = silu_of<T>(from_raw<T>(fetched[j]));
+            else if (k >= 2 * NP + kChannels) v = from_raw<T>(fetched[j]);
+            else if (k >= 2 * NP) v = softplus_of<T>(__uint_as_float(fetched[j]) + bias_mem[k - 2 * NP]);
+            else v = from_raw<T>(fetched[j]);
+            dst[e] = v;
+        }
+    };
 
-    if (row0 < row1) THN_SCAN_LOAD(row0, bc_, cc, dtc, xc, zc);
-    for (int row = row0; row < row1; ++row) {
-        if (row + 1 < row1) THN_SCAN_LOAD(row + 1, bn, cn, dtn, xn, zn);
-        const float dt = softplus_of<T>(dtc + bias);
-        const float xv = xc;
+    if (row1 - row0 == 1) {
+        // a single token: straight from global memory, no stage and no barrier
+        const float dt = softplus_of<T>(dt_pre[(size_t)row0 * channels + c] + dt_bias[c]);     // (bias_mem is not read here)
+        const float xv = to_f32<T>(x[(size_t)row0 * channels + c]);
         const float dx = dt * xv;
         float part = 0.f;
 #pragma unroll
         for (int i = 0; i < PER; ++i) {
-            s[i] = exp_of<T>(dt * a[i]) * s[i] + dx * bc_[i];
-            part += s[i] * cc[i];
+            const int n = lane + kLanes * i;
+            const bool in = n < n_state;
+            const float b = in ? to_f32<T>(bc[(size_t)row0 * bc_width + n]) : 0.f;
+            const float cc = in ? to_f32<T>(bc[(size_t)row0 * bc_width + n_state + n]) : 0.f;
+            s[i] = exp_of<T>(dt * a[i]) * s[i] + dx * b;
+            part += s[i] * cc;
+            if (in && live) S[n] = s[i];
         }
 #pragma unroll
         for (int off = kLanes / 2; off > 0; off >>= 1) part += __shfl_xor_sync(0xffffffffu, part, off);
         if (lane == 0 && live)
-            y[(size_t)row * channels + c] = from_f32<T>((part + skip * xv) * silu_of<T>(zc));
-#pragma unroll
-        for (int i = 0; i < PER; ++i) {
-            bc_[i] = bn[i];
-            cc[i] = cn[i];
-        }
-        dtc = dtn; xc = xn; zc = zn;
+            y[(size_t)row0 * channels + c] = from_f32<T>((part + skip * xv) * silu_of<T>(to_f32<T>(z[(size_t)row0 * z_stride + c])));
+        return;
     }
-#undef THN_SCAN_LOAD
+    if (row0 < row1) fetch(row0);
+    __syncthreads();                                   // the channels' biases are in place
+    if (row0 < row1) publish(0, min(kStage, row1 - row0));
+    __syncthreads();
+    for (int first = row0, buf = 0; first < row1; first += kStage, buf ^= 1) {
+        const bool more = first + kStage < row1;
+        if (more) fetch(first + kStage);
+        // the loads stay here, ahead of the stage's work: sunk to where their values are stored, each
+        // would wait for memory in its turn
+        asm volatile("" ::: "memory");
+        const float* src = stage_mem + buf * kStage * ROW;
+        const int n_tokens = min(kStage, row1 - first);
+        // (unrolled: only the state's multiply-add links one token to the next; the loads, the
+        // exponentials and the shuffles of several tokens then overlap)
+#pragma unroll 4
+        for (int t = 0; t < n_tokens; ++t) {
+            const float* tok = src + t * ROW;
+            const float dt = tok[2 * NP + group], xv = tok[2 * NP + kChannels + group];
+            const float dx = dt * xv;
+            float part = 0.f;
+#pragma unroll
+            for (int i = 0; i < PER; ++i) {
+                const int n = lane + kLanes * i;
+                s[i] = exp_of<T>(dt * a[i]) * s[i] + dx * tok[n];
+                part += s[i] * tok[NP + n];
+            }
+#pragma unroll
+            for (int off = kLanes / 2; off > 0; off >>= 1) part += __shfl_xor_sync(0xffffffffu, part, off);
+            if (lane == 0 && live)
+                y[(size_t)(first + t) * channels + c] = from_f32<T>((part + skip * xv) * tok[2 * NP + 2 * kChannels + group]);
+        }
+        if (more) publish(buf ^ 1, min(kStage, row1 - first - kStage));
+        __syncthreads();
+    }
     if (live && row0 < row1) {
 #pragma unroll
         for (int i = 0; i < PER; ++i) {
@@ -153,17 +234,17 @@ template <typename T>
 int launch_scan(void* y, float* state, const void* x, const float* dt_pre, const float* dt_bias, const void* bc,
                 int bc_width, const float* A, const float* D, const void* z, int z_stride, const int* cu_seqlens,
                 const int* slots, int n_seqs, int channels, int n_state, cudaStream_t stream) {
-    const dim3 grid((channels + kChannels - 1) / kChannels, n_seqs);
-    const int per = (n_state + kLanes - 1) / kLanes;
-#define THN_SCAN_LAUNCH(P)                                                                                              \
-    thn_launch_ordered(selective_scan_kernel<T, P>, grid, kThreads, 0, stream, (T*)y, state, (const T*)x, dt_pre, dt_bias, \
-                       (const T*)bc, bc_width, A, D, (const T*)z, z_stride, cu_seqlens, slots, channels, n_state)
-    if (per <= 1) THN_SCAN_LAUNCH(1);
-    else if (per <= 2) THN_SCAN_LAUNCH(2);
-    else if (per <= 4) THN_SCAN_LAUNCH(4);
-    else if (per <= 8) THN_SCAN_LAUNCH(8);
-    else if (per <= 16) THN_SCAN_LAUNCH(16);
-    else THN_SCAN_LAUNCH(32);
+#define THN_SCAN_LAUNCH(L, P)                                                                                           \
+    thn_launch_ordered(selective_scan_kernel<T, L, P, (kStage * (2 * L * P + 3 * (kScanThreads / L)) + kScanThreads - 1) / kScanThreads>, \
+                       dim3((channels + kScanThreads / L - 1) / (kScanThreads / L), n_seqs), kScanThreads, 0, stream, (T*)y, state, \
+                       (const T*)x, dt_pre, dt_bias, (const T*)bc, bc_width, A, D, (const T*)z, z_stride, cu_seqlens, slots, \
+                       channels, n_state)
+    if (n_state <= 4) THN_SCAN_LAUNCH(4, 1);
+    else if (n_state <= 8) THN_SCAN_LAUNCH(4, 2);
+    else if (n_state <= 16) THN_SCAN_LAUNCH(4, 4);
+    else if (n_state <= 32) THN_SCAN_LAUNCH(4, 8);
+    else if (n_state <= 64) THN_SCAN_LAUNCH(8, 8);
+    else THN_SCAN_LAUNCH(8, 16);
 #undef THN_SCAN_LAUNCH
     return thn_launch_status("selective_scan");
 }
@@ -224,7 +305,7 @@ THN_API int thn_selective_scan(void* y, float* state, const void* x, const float
                                cudaStream_t stream) {
     THN_CHECK_ARG(n_seqs >= 0 && channels > 0 && n_state > 0 && bc_width >= 2 * n_state && z_stride >= channels,
                   "selective_scan: bad sizes");
-    THN_UNSUPPORTED_IF(n_state > 256, "selective_scan: a state of %d per channel, at most 256", n_state);
+    THN_UNSUPPORTED_IF(n_state > 128, "selective_scan: a state of %d per channel, at most 128", n_state);
     THN_UNSUPPORTED_IF(n_seqs > 65535, "selective_scan: %d sequences", n_seqs);
     if (n_seqs == 0) return THN_OK;
     if (dtype == THN_F32)

@@ -63,8 +63,9 @@ _SIGNATURES = {
                             c_int, c_longlong, c_float, c_int, c_void_p],
     "thn_hyper_norm": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float,
                        c_int, c_int, c_int, c_int, c_void_p],
-    "thn_linear_attention": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p,
-                             c_float, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_void_p],
+    "thn_linear_attention": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int,
+                             c_void_p, c_float, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
+                             c_int, c_void_p],
     "thn_causal_conv": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                         c_int, c_int, c_int, c_int, c_void_p],
     "thn_conv_ring_update": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
@@ -169,6 +170,8 @@ def lib():
         loaded.thn_choose_tokens_scratch_floats.restype = c_longlong
         loaded.thn_attention_decode_scratch_floats.argtypes = [c_int, c_int, c_int, c_int]
         loaded.thn_attention_decode_scratch_floats.restype = c_longlong
+        loaded.thn_linear_attention_scratch_floats.argtypes = [c_int, c_int, c_int, c_int, c_int]
+        loaded.thn_linear_attention_scratch_floats.restype = c_longlong
         _lib = loaded
     return _lib
 
@@ -1418,7 +1421,8 @@ def linear_attention(proj: torch.Tensor, offsets: Tuple[int, int, int], state: t
     ``[heads]``, one constant per head) or, per token and key channel,
     ``logistic(gate + gate_bias) ** (1 / tau)`` with ``gate`` float32 ``[rows, >= heads * key_dim]``.
     ``state`` float32 [slots, heads, value_dim, key_dim] is read and updated.  Returns the read-out,
-    float32 [rows, heads, value_dim]."""
+    float32 [rows, heads, value_dim].  Two kernels: the inputs' activations and the decays once per
+    entry into float32 scratch rows, then the recurrence."""
     _need(proj, "linear_attention proj")
     _need(state, "linear_attention state", torch.float32)
     if (decay is None) == (gate is None):
@@ -1439,9 +1443,12 @@ def linear_attention(proj: torch.Tensor, offsets: Tuple[int, int, int], state: t
             if gate_bias.shape[0] != n_heads * key_dim:
                 raise KernelError(f"linear_attention: gate bias {tuple(gate_bias.shape)}")
     o = torch.empty((rows.n_rows, n_heads, value_dim), dtype=torch.float32, device=proj.device)
-    _call("thn_linear_attention", _ptr(o), _ptr(state), _ptr(proj), proj.shape[1], int(offsets[0]), int(offsets[1]),
+    mode = 0 if decay is not None else 1
+    scratch = torch.empty(lib().thn_linear_attention_scratch_floats(rows.n_rows, n_heads, key_dim, value_dim, mode),
+                          dtype=torch.float32, device=proj.device)
+    _call("thn_linear_attention", _ptr(o), _ptr(state), _ptr(scratch), _ptr(proj), proj.shape[1], int(offsets[0]), int(offsets[1]),
           int(offsets[2]), _ptr(decay), _ptr(gate), gate.shape[1] if gate is not None else 0, _ptr(gate_bias), float(tau),
-          _ptr(rows.cu_seqlens), _ptr(rows.slots), rows.n_seqs, n_heads, key_dim, value_dim, float(q_scale),
+          _ptr(rows.cu_seqlens), _ptr(rows.slots), rows.n_rows, rows.n_seqs, n_heads, key_dim, value_dim, float(q_scale),
           0 if decay is not None else 1, int(bool(silu_inputs)), _code(proj, "linear_attention"), _stream())
     return o
 
