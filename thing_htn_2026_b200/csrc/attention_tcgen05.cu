@@ -204,7 +204,7 @@ __global__ void __launch_bounds__(kThreads, 2) attention_tcgen05_kernel(
     __nv_bfloat16* __restrict__ out, const int* __restrict__ tile_row0, const int* __restrict__ tile_rows,
     const int* __restrict__ row_slot, const int* __restrict__ row_pos, const int* __restrict__ block_table,
     int bt_stride, int n_kv, int n_q, float scale_log2, int window, int keep_first, int chunk, ScoreShape shape,
-    int* __restrict__ err) {
+    const float* __restrict__ sinks, int* __restrict__ err) {
     pdl_launch_dependents();
     pdl_wait();
     extern __shared__ __align__(1024) unsigned char smem_raw[];      // swizzled tiles want 1024-byte alignment
@@ -363,7 +363,9 @@ __global__ void __launch_bounds__(kThreads, 2) attention_tcgen05_kernel(
         const float cap_mul = shape.cap > 0.f ? row_factor / (kLog2e * shape.cap) : 0.f;
         const float cap_post = shape.cap * kLog2e;
         const float row_mul = shape.cap > 0.f ? 1.0f : row_factor;
-        float run_max = -INFINITY, run_sum = 0.f;
+        // With sinks the softmax's denominator of head h also holds exp(sinks[h]), a term without key
+        // and value: the row starts from it as its reference point, with the term's 1 in its sum.
+        float run_max = sinks ? sinks[h] * kLog2e : -INFINITY, run_sum = sinks ? 1.0f : 0.f;
         bool ok = true;
         int it = 0;
         for (; it < n_visits && !*give_up; ++it) {
@@ -557,7 +559,7 @@ THN_API int thn_attention_prefill_tcgen05(void* out, const void* q, const int* t
                                           const void* kv_base, long long n_pages, const int* block_table,
                                           int bt_stride, int n_kv, int page_size, int head_dim, int n_q, float scale,
                                           int window, int keep_first, int chunk, float softcap, float temp_coef,
-                                          int temp_every, int* err, cudaStream_t stream) {
+                                          int temp_every, const float* sinks, int* err, cudaStream_t stream) {
     THN_CHECK_ARG(n_tiles >= 0 && n_q > 0 && n_rows_total >= 0 && n_pages > 0 && keep_first >= 0 && chunk >= 0,
                   "attention_tcgen05: bad sizes");
     THN_CHECK_ARG(softcap >= 0.f && temp_every >= 0, "attention_tcgen05: a score cap and a temperature period are not negative");
@@ -589,6 +591,6 @@ THN_API int thn_attention_prefill_tcgen05(void* out, const void* q, const int* t
     dim3 grid(n_q, n_tiles);
     thn_launch(attention_tcgen05_kernel, grid, kThreads, kSmemBytes, stream, map_q, map_kv, (__nv_bfloat16*)out,
                tile_row0, tile_rows, row_slot, row_pos, block_table, bt_stride, n_kv, n_q, scale * kLog2e, window,
-               window > 0 ? keep_first : 0, chunk, ScoreShape{softcap, temp_coef, temp_every}, err);
+               window > 0 ? keep_first : 0, chunk, ScoreShape{softcap, temp_coef, temp_every}, sinks, err);
     return thn_launch_status("attention_tcgen05");
 }

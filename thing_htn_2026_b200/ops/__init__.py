@@ -131,7 +131,7 @@ _SIGNATURES = {
     "thn_attention_tcgen05_test_skip_loads": [c_int],
     "thn_attention_prefill_tcgen05": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p,
                                       c_void_p, c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
-                                      c_int, c_int, c_int, c_float, c_float, c_int, c_void_p, c_void_p],
+                                      c_int, c_int, c_int, c_float, c_float, c_int, c_void_p, c_void_p, c_void_p],
 }
 
 _lib = None
@@ -892,8 +892,8 @@ def attention(q: torch.Tensor, rows: StepRows, kv: KVView, n_q: int, scale: floa
     prompts to the latter.  ``shape``: a position-dependent factor on a row's scores and a tanh
     cap (:class:`ScoreShape`), taken by every kernel but the streaming decode kernel.  ``sinks``: a
     term ``exp(sinks[h])`` without key and value in the softmax's denominator of head h; the
-    warp-per-(row, head) kernel and the ``mma.sync`` kernels take it (the tcgen05 prompt kernel and
-    the streaming decode kernel do not, and are not chosen then)."""
+    warp-per-(row, head) kernel, the ``mma.sync`` kernels and the tcgen05 prompt kernel take it (the
+    streaming decode kernel does not, and is not chosen then)."""
     keep_first = int(keep_first or 0) if window else 0
     if kv.v_dim != kv.head_dim:
         return attention_generic(q, rows, kv, n_q, scale, window, err, keep_first, chunk, exact_weights, shape, sinks)
@@ -902,9 +902,8 @@ def attention(q: torch.Tensor, rows: StepRows, kv: KVView, n_q: int, scale: floa
             return attention_decode_bf16(q, rows, kv, n_q, scale, window, err, keep_first=keep_first, chunk=chunk,
                                          split_weights=exact_weights, shape=shape, sinks=sinks)
         if tiles is not None:
-            if (sinks is None and USE_TCGEN05_ATTENTION
-                    and lib().thn_attention_tcgen05_supported(kv.head_dim, kv.page_size, n_q, kv.n_kv)):
-                return attention_prefill_tcgen05(q, rows, tiles, kv, n_q, scale, window, err, keep_first, chunk, shape)
+            if USE_TCGEN05_ATTENTION and lib().thn_attention_tcgen05_supported(kv.head_dim, kv.page_size, n_q, kv.n_kv):
+                return attention_prefill_tcgen05(q, rows, tiles, kv, n_q, scale, window, err, keep_first, chunk, shape, sinks)
             return attention_prefill_bf16(q, rows, tiles, kv, n_q, scale, window, err, keep_first, chunk, exact_weights,
                                           shape, sinks)
     return attention_generic(q, rows, kv, n_q, scale, window, err, keep_first, chunk, exact_weights, shape, sinks)
@@ -912,7 +911,8 @@ def attention(q: torch.Tensor, rows: StepRows, kv: KVView, n_q: int, scale: floa
 
 def attention_prefill_tcgen05(q: torch.Tensor, rows: StepRows, tiles: RowTiles, kv: KVView, n_q: int, scale: float,
                               window: Optional[int], err: torch.Tensor, keep_first: int = 0,
-                              chunk: Optional[int] = None, shape: ScoreShape = PLAIN_SCORES) -> torch.Tensor:
+                              chunk: Optional[int] = None, shape: ScoreShape = PLAIN_SCORES,
+                              sinks: Optional[torch.Tensor] = None) -> torch.Tensor:
     """tcgen05 / TMEM / TMA flash attention for steps with several tokens per sequence
     (bfloat16, head size 128)."""
     _need(q, "attention q", torch.bfloat16)
@@ -921,7 +921,7 @@ def attention_prefill_tcgen05(q: torch.Tensor, rows: StepRows, tiles: RowTiles, 
     _call("thn_attention_prefill_tcgen05", _ptr(out), _ptr(q), _ptr(tiles.row0), _ptr(tiles.rows),
           tiles.n, q.shape[0], _ptr(rows.row_slot), _ptr(rows.row_pos), _ptr(kv.storage), kv.storage.shape[0],
           _ptr(kv.block_table), kv.block_table.shape[1], kv.n_kv, kv.page_size, kv.head_dim, n_q, float(scale),
-          int(window or 0), int(keep_first or 0), int(chunk or 0), *shape.args(), _ptr(err), _stream())
+          int(window or 0), int(keep_first or 0), int(chunk or 0), *shape.args(), _ptr(sinks), _ptr(err), _stream())
     return out
 
 
