@@ -74,6 +74,18 @@ __global__ void conv_ring_update_kernel(T* __restrict__ ring, const T* __restric
     }
 }
 
+// The decay exp(dt * A).  With bfloat16 activations A is held times log2(e) and the exponential is
+// the hardware's base-2 one (two ulp; four full ones a token are a third of the scan's instructions
+// otherwise); on the 32-bit path it is computed in double and rounded once.
+template <typename T> struct Decay {
+    static __device__ __forceinline__ float hold(float a) { return a * 1.4426950408889634f; }
+    static __device__ __forceinline__ float of(float dt, float held) { return exp2f(dt * held); }
+};
+template <> struct Decay<float> {
+    static __device__ __forceinline__ float hold(float a) { return a; }
+    static __device__ __forceinline__ float of(float dt, float held) { return exp_of<float>(dt * held); }
+};
+
 // LANES lanes hold a channel's state, PER entries each; NP = LANES * PER: the padded state size of a
 // staged token's B and C.  A block of 256 threads takes 256 / LANES channels: 64 with four lanes
 // (states up to 32), so that a token's step sizes, inputs and gates are runs of 128 to 256 bytes.
@@ -122,7 +134,7 @@ __global__ void __launch_bounds__(kScanThreads) selective_scan_kernel(
     for (int i = 0; i < PER; ++i) {
         const int n = lane + kLanes * i;
         s[i] = n < n_state ? S[n] : 0.f;
-        a[i] = n < n_state ? A[(size_t)c * n_state + n] : 0.f;
+        a[i] = n < n_state ? Decay<T>::hold(A[(size_t)c * n_state + n]) : 0.f;
     }
     const float skip = D[c];
     if (threadIdx.x < kChannels) bias_mem[threadIdx.x] = dt_bias[min(c0 + (int)threadIdx.x, channels - 1)];
@@ -177,7 +189,7 @@ __global__ void __launch_bounds__(kScanThreads) selective_scan_kernel(
             const bool in = n < n_state;
             const float b = in ? to_f32<T>(bc[(size_t)row0 * bc_width + n]) : 0.f;
             const float cc = in ? to_f32<T>(bc[(size_t)row0 * bc_width + n_state + n]) : 0.f;
-            s[i] = exp_of<T>(dt * a[i]) * s[i] + dx * b;
+            s[i] = Decay<T>::of(dt, a[i]) * s[i] + dx * b;
             part += s[i] * cc;
             if (in && live) S[n] = s[i];
         }
@@ -210,7 +222,7 @@ __global__ void __launch_bounds__(kScanThreads) selective_scan_kernel(
 #pragma unroll
             for (int i = 0; i < PER; ++i) {
                 const int n = lane + kLanes * i;
-                s[i] = exp_of<T>(dt * a[i]) * s[i] + dx * tok[n];
+                s[i] = Decay<T>::of(dt, a[i]) * s[i] + dx * tok[n];
                 part += s[i] * tok[NP + n];
             }
 #pragma unroll
