@@ -30,7 +30,8 @@ config.json keys::
                           left_scale, right_scale: the weights of their sum.
     mixer of "gla":       heads, dim, vdim, tau: linear attention with a decay per key channel
                           ``logistic(z)^(1/tau)``, z through a low-rank pair of projections; RMS norm per head,
-                          a silu gate.
+                          a silu gate.  ``rank`` (optional): the channels between the two projections; without it the
+                          shapes of the checkpoint's two tensors give it (random weights need it).
     mixer of "mamba1":    inner, state, dt_rank, conv: the selective scan behind a short causal convolution.
 
 Tensor names: layer i's start with ``l<i>.``; its norms are ``norm1`` and ``norm2`` (one number each), its

@@ -73,8 +73,9 @@ class GatedAttention(PhasedMixer):
         _, self.n_q, self.n_kv, self.head_dim, self.value_dim = self._sizes(spec)
         if self.n_q % self.n_kv:
             raise ValueError(f"gated_attention: {self.n_q} heads are not a multiple of {self.n_kv} kv heads")
-        if p.get("gate") not in (None, "logistic"):
-            raise ValueError(f"gated_attention: gate {p.get('gate')!r} is not 'logistic'")
+        if p.get("gate") != "logistic":
+            raise ValueError(f"gated_attention: gate {p.get('gate')!r}; the read-out is turned back and scaled in the "
+                             f"logistic gate's kernel, so the gate is 'logistic'")
         self.scale = float(p["scale"])
         self.eps = None if p.get("qk_norm_eps") is None else float(p["qk_norm_eps"])
         self.window = None if p.get("window") is None else int(p["window"])
@@ -109,7 +110,7 @@ class GatedAttention(PhasedMixer):
     def _tile(self, page_size: int) -> int:
         return ops.prompt_attention_tile(self.dtype, self.head_dim, page_size, self.n_q, self.n_kv, self.value_dim)
 
-    def step_inputs(self, batch, out) -> None:
+    def step_inputs(self, batch: HostBatch, out) -> None:
         """The row tiles of the tensor-core prompt kernel, where the sizes go to it (keys and values
         of one size that it takes); every attention that wants tiles of one size shares one list."""
         size = self._tile(batch.page_size) if batch.max_count > 1 else 0
@@ -131,8 +132,5 @@ class GatedAttention(PhasedMixer):
                            proj_offset=offset)
         a = ops.attention(q, ctx.rows, kv, self.n_q, self.scale, self.window, ctx.err, tiles, exact_weights=True,
                           sinks=self.sinks)
-        if self.gated:
-            ops.rotate_gate(a, proj, offset + self.gate_offset, self.n_q, self.value_dim, turn, ctx.rows, ctx.err, scale,
-                            out, out_offset)
-        else:
-            raise NotImplementedError("gated_attention: the read-out is turned back in the gate's kernel")
+        ops.rotate_gate(a, proj, offset + self.gate_offset, self.n_q, self.value_dim, turn, ctx.rows, ctx.err, scale, out,
+                        out_offset)
